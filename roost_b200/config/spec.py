@@ -14,6 +14,8 @@ from dataclasses import dataclass, field
 
 @dataclass(frozen=True)
 class NormSpec:
+    """``rms_norm``: x / sqrt(mean(x^2) + eps) * w. ``layer_norm``: (x - mean) / sqrt(var + eps) * w + b, var the mean squared
+    deviation; it reads a 32-bit stream and writes the activation dtype."""
     size: int
     eps: float
     kind: str = "rms_norm"
@@ -50,6 +52,47 @@ class AttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Causal attention whose keys and values are made per head from one latent vector a token: the cache keeps the
+    latent (``kv_rank`` numbers, unit root mean square times a weight) and one rotated key part of ``rope_dim`` numbers
+    that all heads share. A head's key is [W_uk c | shared part] against a query of ``nope_dim`` plain and ``rope_dim``
+    rotated numbers, its value W_uv c of ``v_dim`` numbers. ``window`` counts the keys a query sees, its own included
+    (None: all). ``own_latent`` False: the run makes no latent and reads another run's; ``cache_window`` is then the
+    window the shared cache is kept for (the widest of the runs that read it; None: everything is kept)."""
+    kind: str = "latent_attention"
+    hidden: int = 0
+    num_heads: int = 0
+    nope_dim: int = 0
+    rope_dim: int = 0
+    v_dim: int = 0
+    kv_rank: int = 0
+    scale: float = 0.0
+    window: int | None = None
+    cache_window: int | None = None
+    own_latent: bool = True
+    latent_eps: float = 1e-6
+    position: PositionSpec | None = None
+
+
+@dataclass(frozen=True)
+class Mamba2Spec(MixerSpec):
+    """The Mamba-2 recurrence. The input projection gives [z | x | B | C | dt]; x, B and C pass a causal convolution of
+    ``conv_taps`` taps a channel and SiLU; per head (``head_dim`` values, state ``state`` x ``head_dim``, B and C shared by
+    the heads of one of ``groups`` groups) S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x with dt = softplus(dt +
+    dt_bias); y SiLU(z) is divided by its root mean square in ``norm_groups`` equal parts, times a weight, and projected
+    out. The state and the last ``conv_taps`` - 1 inputs of the convolution are kept per request in 32-bit."""
+    kind: str = "mamba2"
+    hidden: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    state: int = 0
+    groups: int = 1
+    conv_taps: int = 4
+    norm_groups: int = 1
+    eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str = ""
 
@@ -61,6 +104,25 @@ class GatedMlpSpec(FeedForwardSpec):
     hidden: int = 0
     intermediate: int = 0
     activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class RoutedMlpSpec(FeedForwardSpec):
+    """``experts`` gated feed-forwards of ``expert_intermediate`` rows of which a token uses the ``top`` with the largest
+    router scores, and a shared one of ``shared_intermediate`` rows (0: none) that every token uses. ``score``: the
+    function that turns router logits into scores ("sigmoid"); ``renormalize``: whether the chosen scores are divided by
+    their sum; ``weight_on``: "input" when a chosen expert is given score * x (the sum of expert(score x)), "output" when
+    its output is multiplied."""
+    kind: str = "routed_mlp"
+    hidden: int = 0
+    experts: int = 0
+    top: int = 1
+    expert_intermediate: int = 0
+    shared_intermediate: int = 0
+    activation: str = "silu"
+    score: str = "sigmoid"
+    renormalize: bool = False
+    weight_on: str = "input"
 
 
 @dataclass(frozen=True)
@@ -82,12 +144,28 @@ class HeadSpec:
 
 
 @dataclass(frozen=True)
+class ScaledEmbeddingSpec(EmbeddingSpec):
+    """h0[t, :] = table[ids[t], :] * scale, formed and kept in 32-bit (the stream of a ``pre_norm_wide`` model)."""
+    kind: str = "scaled_table"
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class CappedHeadSpec(HeadSpec):
+    """logits = cap * tanh((final W^T) / cap) in 32-bit."""
+    kind: str = "capped_linear"
+    cap: float = 0.0
+
+
+@dataclass(frozen=True)
 class BlockSpec:
-    """One layer's parts and their arrangement. ``pre_norm``: h += mixer(norm1(h)); h += ff(norm2(h))."""
+    """One layer's parts and their arrangement. ``pre_norm``: h += mixer(norm1(h)); h += ff(norm2(h)), the stream in the
+    activation dtype. ``pre_norm_wide``: the same with the stream kept and summed in 32-bit whatever the activation dtype
+    is; its ``feed_forward`` and ``post_mixer_norm`` may be None (a layer that is its mixer only)."""
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: FeedForwardSpec | None
     input_norm: NormSpec
-    post_mixer_norm: NormSpec
+    post_mixer_norm: NormSpec | None
     kind: str = "pre_norm"
 
 
@@ -116,6 +194,8 @@ class ModelSpec:
     # vocabulary and width)
     embedding: EmbeddingSpec | None = None
     head: HeadSpec | None = None
+    # checkpoint tensors the model does not use and a checkpoint may hold all the same (the loader passes over them)
+    ignorable_tensors: tuple = ()
     # checkpoint tensor names: scope -> {part-local parameter name -> tuple of checkpoint names whose rows
     # are concatenated in order}. Scopes: "embed", "final_norm", "lm_head", "blocks.<i>.<part>".
     weight_names: dict = field(default_factory=dict, compare=False, hash=False)

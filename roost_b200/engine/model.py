@@ -144,7 +144,7 @@ def load_model(model_dir, dtype: torch.dtype, device="cuda", kernels=None) -> Mo
     runtime = Runtime(dtype, device, kernels if kernels is not None else library.load())
     model = Model(spec, runtime)
     decls = parameter_declarations(spec)
-    allow = ("lm_head.weight",) if spec.tie_embeddings else ()
+    allow = (("lm_head.weight",) if spec.tie_embeddings else ()) + tuple(spec.ignorable_tensors)
     params = weight_loader.load_checkpoint(model_dir, decls, spec.weight_names, allow_unexpected=allow)
     model.load(params)
     model.config = cfg

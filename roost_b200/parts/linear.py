@@ -59,3 +59,14 @@ class Linear:
             k.library_launches += 1
             return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
         return k.gemm_simt(x, self.weight, torch.float32)
+
+
+def batched_linear(rt: Runtime, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[b] = a[b] w[b]^T for a [B, M, K], w [B, N, K] (contiguous) and out [B, M, N]; ``a`` and ``out`` may be views whose
+    rows and batches are strided (heads side by side in a token's row) as long as their last dimension is dense: no
+    operand is copied. float32 runs the library's FFMA product over the batch, bfloat16 cuBLAS's strided batched product
+    with 32-bit accumulation."""
+    if rt.full_precision:
+        return rt.kernels.gemm_simt_batched(a, w, out)
+    rt.kernels.library_launches += 1
+    return torch.bmm(a, w.transpose(1, 2), out=out)

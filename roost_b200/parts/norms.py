@@ -1,6 +1,6 @@
 """RMS norm: y = x / sqrt(mean(x^2) + eps) * w with the weight as stored
 (src/Starlings.Roost.Ops/CpuOps.cs:87-101), alone or fused with the residual sum that precedes it
-(src/Starlings.Roost.Ops/CpuOps.Fused.cs:26-34)."""
+(src/Starlings.Roost.Ops/CpuOps.Fused.cs:26-34). And the layer norm with weight and bias over a 32-bit stream."""
 from __future__ import annotations
 
 import torch
@@ -33,4 +33,34 @@ class RmsNorm(Norm):
         return out, residual
 
 
+class LayerNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * w + b over a 32-bit stream; the output has the activation dtype. ``add_norm`` adds a
+    branch output (activation dtype) to the stream in 32-bit first: the stream is never rounded."""
+
+    def __init__(self, spec: NormSpec, runtime: Runtime):
+        if spec.size <= 0 or spec.eps <= 0:
+            raise ValueError(f"layer_norm: size {spec.size} and eps {spec.eps} must be positive")
+        self.spec = spec
+        self.rt = runtime
+        self.weight: torch.Tensor | None = None
+        self.bias: torch.Tensor | None = None
+
+    @classmethod
+    def parameters(cls, spec: NormSpec):
+        return {"weight": ParamDecl(shape=(spec.size,), role="vector"), "bias": ParamDecl(shape=(spec.size,), role="vector")}
+
+    def load(self, params):
+        self.weight = params["weight"].float().contiguous()
+        self.bias = params["bias"].float().contiguous()
+
+    def __call__(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return self.rt.kernels.layer_norm(x, self.weight, self.bias, self.spec.eps, self.rt.dtype, None, rows)
+
+    def add_norm(self, x: torch.Tensor, residual: torch.Tensor, rows: torch.Tensor | None = None):
+        """Returns (norm(residual + x), residual + x); without ``rows`` the sum replaces ``residual`` in place."""
+        out = self.rt.kernels.layer_norm(residual, self.weight, self.bias, self.spec.eps, self.rt.dtype, x, rows)
+        return out, residual
+
+
 register_norm("rms_norm", RmsNorm)
+register_norm("layer_norm", LayerNorm)

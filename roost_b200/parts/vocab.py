@@ -59,5 +59,26 @@ class LinearHead(Head):
         return self.linear(final, out_dtype=torch.float32)
 
 
+class ScaledTableEmbedding(TableEmbedding):
+    """h0[t, :] = table[ids[t], :] * scale as a float32 stream (the product is formed in 32-bit and not rounded)."""
+
+    def __call__(self, ids, batch=None):
+        return self.rt.kernels.embedding_scaled(self.table, ids, float(self.spec.scale))
+
+
+class CappedLinearHead(LinearHead):
+    """cap * tanh(logits / cap) on the 32-bit logits."""
+
+    def __init__(self, spec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        if not spec.cap > 0:
+            raise ValueError(f"capped_linear: cap {spec.cap} must be positive")
+
+    def __call__(self, final, batch=None):
+        return self.rt.kernels.softcap_(self.linear(final, out_dtype=torch.float32), float(self.spec.cap))
+
+
 register_embedding("table", TableEmbedding)
+register_embedding("scaled_table", ScaledTableEmbedding)
+register_head("capped_linear", CappedLinearHead)
 register_head("linear", LinearHead)

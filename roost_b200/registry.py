@@ -2,7 +2,7 @@
 
 An entry knows how to read the architecture's config.json into a typed configuration and how to turn that
 into a ``ModelSpec`` (parts, run order, checkpoint names). The model class is chosen by config.json everywhere
-in the package: ``architectures[0]`` first, ``model_type`` second. The reference binds a model id to a model in
+in the package: ``architectures`` (or the single string ``architecture``) first, ``model_type`` second. The reference binds a model id to a model in
 its worker (src/Starlings.Roost.Worker.Runtime/Program.cs:28-33) and names the served ids when the id is
 unknown; an unknown architecture here lists the registered ones.
 
@@ -41,6 +41,9 @@ def registered() -> list[str]:
 
 def resolve(reader: ConfigReader) -> Architecture:
     names = reader.opt_strs("architectures") or []
+    single = reader.opt_str("architecture")      # a config.json that names its one architecture as a string
+    if single is not None:
+        names = names + [single]
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
@@ -54,7 +57,8 @@ def resolve(reader: ConfigReader) -> Architecture:
 
 
 def _register_builtin() -> None:
-    from .config import qwen3
+    from .config import qwen3, vamatar
+    register_architecture(vamatar.ARCHITECTURE, read_config=vamatar.VamatarConfig.from_reader, to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
     register_architecture(qwen3.ARCHITECTURE, model_types=(qwen3.MODEL_TYPE,), read_config=qwen3.Qwen3Config.from_reader,
                           to_spec=lambda cfg, tied=None: cfg.to_spec(tied), reference_slots=lambda cfg: cfg.reference_slots())
 

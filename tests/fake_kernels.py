@@ -96,6 +96,162 @@ class FakeKernels:
                 out[t, h * d : (h + 1) * d] = (p @ vv[:, h // group, :]).to(q.dtype)
         return out
 
+    # ---- the wide stream's ends and norm
+    def embedding_scaled(self, table, ids, scale):
+        return table[ids.long()].float() * scale
+
+    def layer_norm(self, stream, w, b, eps, out_dtype, addend=None, rows=None):
+        s = stream if addend is None else stream + addend.float()
+        if addend is not None and rows is None:
+            stream.copy_(s)
+        if rows is not None:
+            s = s[rows.long()]
+        mu = s.mean(-1, keepdim=True)
+        d = s - mu
+        return (d * torch.rsqrt((d * d).mean(-1, keepdim=True) + eps) * w + b).to(out_dtype)
+
+    def softcap_(self, logits, cap):
+        return logits.copy_(cap * torch.tanh(logits / cap))
+
+    def gemm_simt_batched(self, a, w, out):
+        out.copy_(torch.bmm(a.float(), w.float().transpose(1, 2)).to(out.dtype))
+        return out
+
+    # ---- latent attention
+    def latent_prepare(self, q, down, pool, latent_w, inv_freq, rotary_dim, positions, slot_mapping, heads, nope, rope, rank, eps, page_size):
+        T = q.shape[0]
+        half = rotary_dim // 2
+        ang = positions.double()[:, None] * inv_freq[None, :]
+        c, s = torch.cos(ang).float(), torch.sin(ang).float()
+
+        def turn(v):        # [..., rope] float32, rotated in its first rotary_dim elements
+            u, w2 = v[..., :half].clone(), v[..., half:rotary_dim].clone()
+            shape = [T] + [1] * (v.dim() - 2) + [half]
+            v[..., :half] = u * c.reshape(shape) - w2 * s.reshape(shape)
+            v[..., half:rotary_dim] = w2 * c.reshape(shape) + u * s.reshape(shape)
+            return v
+
+        qv = q.view(T, heads, nope + rope)
+        qv[:, :, nope:] = turn(qv[:, :, nope:].float()).to(q.dtype)
+        if down is not None:
+            lat = down[:, :rank].float()
+            lat = lat * torch.rsqrt((lat * lat).mean(-1, keepdim=True) + eps) * latent_w
+            entry = torch.cat([lat, turn(down[:, rank:].float())], -1).to(pool.dtype)
+            for t in range(T):
+                slot = int(slot_mapping[t])
+                if slot >= 0:
+                    pool[slot // page_size, 0, slot % page_size] = entry[t]
+
+    def latent_attention(self, q_latent, q, pool, positions, token_row, kv_indptr, kv_indices, heads, nope, rope, rank, scale, window, decode_hint=False):
+        T = q.shape[0]
+        page = pool.shape[2]
+        out = torch.zeros(heads, T, rank, dtype=q.dtype)
+        qr = q.view(T, heads, nope + rope)[:, :, nope:].float()
+        for t in range(T):
+            pos, b = int(positions[t]), int(token_row[t])
+            if pos < 0:
+                continue
+            pages = kv_indices[int(kv_indptr[b]) : int(kv_indptr[b + 1])]
+            lo = max(0, pos - window + 1) if window else 0
+            e = torch.stack([pool[int(pages[j // page]), 0, j % page] for j in range(lo, pos + 1)]).float()    # [n, rank + rope]
+            sc = (q_latent[:, t].float() @ e[:, :rank].T + qr[t] @ e[:, rank:].T) * scale                    # [heads, n]
+            out[:, t] = (torch.softmax(sc, -1) @ e[:, :rank]).to(q.dtype)
+        return out
+
+    # ---- mamba-2
+    def mamba2_conv(self, u, col, channels, w, b, state, conv_off, token_row, q_indptr, slots):
+        T, taps = u.shape[0], w.shape[1]
+        out = torch.zeros(T, channels, dtype=torch.float32)
+        for t in range(T):
+            r = int(token_row[t])
+            start, slot = int(q_indptr[r]), int(slots[r])
+            acc = b.clone()
+            for k in range(taps):
+                i = t - (taps - 1) + k
+                if i >= start:
+                    v = u[i, col : col + channels].float()
+                else:
+                    j = i - start + (taps - 1)
+                    v = state[slot, conv_off + j * channels : conv_off + (j + 1) * channels]
+                acc = acc + w[:, k] * v
+            out[t] = acc / (1 + torch.exp(-acc))
+        return out.to(u.dtype)
+
+    def mamba2_conv_state(self, u, col, channels, taps, state, conv_off, q_indptr, slots):
+        keep = taps - 1
+        for r in range(slots.numel()):
+            start, end, slot = int(q_indptr[r]), int(q_indptr[r + 1]), int(slots[r])
+            if end == start:
+                continue
+            old = state[slot, conv_off : conv_off + keep * channels].reshape(keep, channels)
+            both = torch.cat([old, u[start:end, col : col + channels].float()])
+            state[slot, conv_off : conv_off + keep * channels] = both[both.shape[0] - keep :].reshape(-1)
+
+    def mamba2_scan(self, xbc, u, dt_col, dt_bias, a_log, d, state, q_indptr, slots, heads, P, N, groups):
+        T = xbc.shape[0]
+        inner, per = heads * P, heads // groups
+        y = torch.zeros(T, inner, dtype=torch.float32)
+        for r in range(slots.numel()):
+            slot = int(slots[r])
+            S = state[slot, : heads * N * P].reshape(heads, N, P).clone()
+            for t in range(int(q_indptr[r]), int(q_indptr[r + 1])):
+                dt = torch.nn.functional.softplus(u[t, dt_col : dt_col + heads].float() + dt_bias, threshold=30.0)
+                decay = torch.exp(-torch.exp(a_log) * dt)
+                x = xbc[t, :inner].float().reshape(heads, P)
+                B = xbc[t, inner : inner + groups * N].float().reshape(groups, N).repeat_interleave(per, 0)
+                C = xbc[t, inner + groups * N :].float().reshape(groups, N).repeat_interleave(per, 0)
+                S = decay[:, None, None] * S + dt[:, None, None] * B[:, :, None] * x[:, None, :]
+                y[t] = ((S * C[:, :, None]).sum(1) + d[:, None] * x).reshape(-1)
+            state[slot, : heads * N * P] = S.reshape(-1)
+        return y
+
+    def gated_group_norm(self, y, u, w, groups, eps, out_dtype):
+        T, inner = y.shape
+        z = u[:, :inner].float()
+        g = (y * (z / (1 + torch.exp(-z)))).reshape(T, groups, inner // groups)
+        g = g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)
+        return (g.reshape(T, inner) * w).to(out_dtype)
+
+    # ---- routed experts
+    def moe_route(self, logits, top):
+        from types import SimpleNamespace
+        T, E = logits.shape
+        s = torch.sigmoid(logits)
+        pairs = []
+        for t in range(T):
+            for e in sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]:
+                pairs.append((e, t, float(s[t, e])))
+        order = sorted(range(len(pairs)), key=lambda i: (pairs[i][0], i))
+        inverse = torch.zeros(len(pairs), dtype=torch.int32)
+        for dest, i in enumerate(order):
+            inverse[i] = dest
+        return SimpleNamespace(top=top, token=torch.tensor([pairs[i][1] for i in order], dtype=torch.int32),
+                               weight=torch.tensor([pairs[i][2] for i in order], dtype=torch.float32),
+                               expert=[pairs[i][0] for i in order], inverse=inverse)
+
+    def moe_gather_scale(self, x, route):
+        return (x[route.token.long()].float() * route.weight[:, None]).to(x.dtype)
+
+    def moe_expert_gate_up(self, xs, gate, up, route):
+        out = torch.zeros(xs.shape[0], gate.shape[1], dtype=xs.dtype)
+        for i, e in enumerate(route.expert):
+            g, u2 = gate[e].float() @ xs[i].float(), up[e].float() @ xs[i].float()
+            out[i] = (g / (1 + torch.exp(-g)) * u2).to(xs.dtype)
+        return out
+
+    def moe_expert_down(self, act, down, route):
+        out = torch.zeros(act.shape[0], down.shape[1], dtype=act.dtype)
+        for i, e in enumerate(route.expert):
+            out[i] = (down[e].float() @ act[i].float()).to(act.dtype)
+        return out
+
+    def moe_combine(self, ys, route, shared=None):
+        T = ys.shape[0] // route.top
+        out = ys[route.inverse.long()].float().reshape(T, route.top, -1).sum(1)
+        if shared is not None:
+            out = out + shared.float()
+        return out.to(ys.dtype)
+
     def gemm_stream_supported(self, *a):
         return False
 
