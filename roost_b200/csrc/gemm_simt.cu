@@ -11,7 +11,11 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ a, const TIn* __restrict__ w,
                                                        TOut* __restrict__ out, int M, int N, int K, int64_t lda,
-                                                       int64_t ldw, int64_t ldo) {
+                                                       int64_t ldw, int64_t ldo, int64_t batch_a, int64_t batch_w,
+                                                       int64_t batch_o) {
+  a += blockIdx.z * batch_a;   // a batch of products: one grid layer each (strides in elements; 0 for a single product)
+  w += blockIdx.z * batch_w;
+  out += blockIdx.z * batch_o;
   __shared__ float as[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
   const int tid = threadIdx.x;
@@ -64,24 +68,37 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ 
 
 using namespace roost;
 
-extern "C" int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
-                               int64_t ldo, int in_dtype, int out_dtype, roost_stream_t stream) {
-  ROOST_REQUIRE(m >= 0 && n > 0 && k > 0, "gemm: m, n and k must be positive");
+static int launch_gemm_simt(const void* a, const void* w, void* out, int batch, int m, int n, int k, int64_t lda, int64_t ldw, int64_t ldo,
+                            int64_t batch_a, int64_t batch_w, int64_t batch_o, int in_dtype, int out_dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(m >= 0 && n > 0 && k > 0 && batch >= 0, "gemm: m, n and k must be positive");
   ROOST_REQUIRE(lda >= k && ldw >= k && ldo >= n, "gemm: a leading dimension is smaller than its row");
-  if (m == 0) return ROOST_OK;
-  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM);
+  if (m == 0 || batch == 0) return ROOST_OK;
+  dim3 grid((n + BN - 1) / BN, (m + BM - 1) / BM, batch);
   if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "gemm: more than 4194240 rows in one product");
+  if (batch > 65535) return fail(ROOST_ERR_UNSUPPORTED, "gemm: more than 65535 products in one batch");
   cudaStream_t s = (cudaStream_t)stream;
   if (in_dtype == ROOST_F32 && out_dtype == ROOST_F32) {
-    gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>((const float*)a, (const float*)w, (float*)out, m, n, k, lda, ldw, ldo);
+    gemm_simt_kernel<float, float><<<grid, 256, 0, s>>>((const float*)a, (const float*)w, (float*)out, m, n, k, lda, ldw, ldo, batch_a,
+                                                        batch_w, batch_o);
   } else if (in_dtype == ROOST_BF16 && out_dtype == ROOST_BF16) {
     gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w,
-                                                                       (__nv_bfloat16*)out, m, n, k, lda, ldw, ldo);
+                                                                       (__nv_bfloat16*)out, m, n, k, lda, ldw, ldo, batch_a, batch_w, batch_o);
   } else if (in_dtype == ROOST_BF16 && out_dtype == ROOST_F32) {
     gemm_simt_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (float*)out,
-                                                               m, n, k, lda, ldw, ldo);
+                                                               m, n, k, lda, ldw, ldo, batch_a, batch_w, batch_o);
   } else {
     return fail(ROOST_ERR_INVALID, "gemm: dtype codes must be (0,0), (1,1) or (1,0) for (in, out)");
   }
   return check_launch("gemm_simt");
+}
+
+extern "C" int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
+                               int64_t ldo, int in_dtype, int out_dtype, roost_stream_t stream) {
+  return launch_gemm_simt(a, w, out, 1, m, n, k, lda, ldw, ldo, 0, 0, 0, in_dtype, out_dtype, stream);
+}
+
+extern "C" int roost_gemm_simt_batched(const void* a, const void* w, void* out, int batch, int m, int n, int k, int64_t lda, int64_t ldw,
+                                       int64_t ldo, int64_t batch_a, int64_t batch_w, int64_t batch_o, int in_dtype, int out_dtype,
+                                       roost_stream_t stream) {
+  return launch_gemm_simt(a, w, out, batch, m, n, k, lda, ldw, ldo, batch_a, batch_w, batch_o, in_dtype, out_dtype, stream);
 }

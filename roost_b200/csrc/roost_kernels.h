@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 11
+#define ROOST_ABI_VERSION 12
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -241,6 +241,64 @@ int roost_sample_count_tokens(int32_t* counts, int vocab, const int32_t* row_slo
 int roost_sample_prompt_bits(uint32_t* bits, const int32_t* ids, int n, int vocab, roost_stream_t stream);
 int roost_sample_logprobs(const float* logits, int64_t stride, int rows, int vocab, const int32_t* ids, float* logprob, int top,
                           int32_t* top_ids, float* top_vals, roost_stream_t stream);
+
+/* ---- a model whose residual stream is kept in 32-bit (wide_stream.cu) ---- */
+/* out[t,:] = table[ids[t],:] * scale as float32; an id outside [0, vocab) gives a zero row. */
+int roost_embedding_scaled(const void* table, const int32_t* ids, float* out, int tokens, int hidden, int vocab, float scale,
+                           int dtype, roost_stream_t stream);
+/* s = stream[r,:] (+ addend[r,:], of the activation dtype, when not null) in 32-bit, r = rows ? rows[i] : i; without rows the
+ * sum is written back to the stream. out[i,:] = (s - mean) / sqrt(var + eps) * w + b in the activation dtype `dtype`. */
+int roost_layer_norm(float* stream, const void* addend, const float* w, const float* b, void* out, const int32_t* rows, int n_out,
+                     int hidden, float eps, int dtype, roost_stream_t stream_handle);
+/* x <- cap * tanh(x / cap) over n floats. */
+int roost_softcap(float* logits, int64_t n, float cap, roost_stream_t stream);
+/* `batch` products out[b] = a[b] w[b]^T on FFMA; the batch strides are in elements (see roost_gemm_simt). */
+int roost_gemm_simt_batched(const void* a, const void* w, void* out, int batch, int m, int n, int k, int64_t lda, int64_t ldw,
+                            int64_t ldo, int64_t batch_a, int64_t batch_w, int64_t batch_o, int in_dtype, int out_dtype,
+                            roost_stream_t stream);
+
+/* ---- latent attention (latent_attention.cu) ---- */
+/* q: [tokens, heads * (nope + rope)], every head's last `rope` elements rotated in place (their first rot_dims elements,
+ * pairs (i, i + rot_dims/2), angle positions[t] * inv_freq[i]). down (may be null): [tokens, rank + rope]; its first `rank`
+ * elements divided by their root mean square (eps inside the root) times latent_w, its last `rope` rotated the same way, go
+ * to pool[slot_mapping[t] * (rank + rope) ..] (a negative slot is skipped). */
+int roost_latent_prepare(void* q, const void* down, void* pool, const float* latent_w, const double* inv_freq,
+                         const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int nope, int rope,
+                         int rot_dims, int rank, float eps, int dtype, roost_stream_t stream);
+/* q_latent: [heads, tokens, rank]; q as above (rotated); pool: [pages, page_size, rank + rope]; out: [heads, tokens, rank] =
+ * sum_j p_j c_j with p the softmax over the visible keys of (q_latent . c_j + q_rot . r_j) * scale. splits > 1 deals a
+ * token's key tiles to that many blocks; part: float[tokens * heads * splits * (rank + 2)]. Tables as in
+ * roost_paged_attention_generic. */
+int roost_latent_attention(const void* q_latent, const void* q, void* out, float* part, const void* pool, const int32_t* positions,
+                           const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens, int heads,
+                           int nope, int rope, int rank, int page_size, float scale, int window, int splits, int dtype,
+                           roost_stream_t stream);
+
+/* ---- the Mamba-2 recurrence (mamba2.cu; the layout of a state slot and the formulas are at the top of that file) ---- */
+int roost_mamba2_conv(const void* u, int64_t ld, int col, void* out, const float* w, const float* bias, const float* state,
+                      int64_t state_stride, int conv_off, const int32_t* token_row, const int32_t* q_indptr, const int32_t* slots,
+                      int tokens, int channels, int taps, int dtype, roost_stream_t stream);
+int roost_mamba2_conv_state(const void* u, int64_t ld, int col, float* state, int64_t state_stride, int conv_off,
+                            const int32_t* q_indptr, const int32_t* slots, int rows, int channels, int taps, int dtype,
+                            roost_stream_t stream);
+int roost_mamba2_scan(const void* xbc, const void* u, int64_t ld_u, int dt_col, float* y, const float* dt_bias, const float* a_log,
+                      const float* d_skip, float* state, int64_t state_stride, const int32_t* q_indptr, const int32_t* slots,
+                      int rows, int heads, int head_dim, int state_rows, int groups, int dtype, roost_stream_t stream);
+int roost_gated_group_norm(const float* y, const void* u, int64_t ld_u, const float* w, void* out, int tokens, int inner, int groups,
+                           float eps, int dtype, roost_stream_t stream);
+
+/* ---- a feed-forward routed over experts (routed_experts.cu) ---- */
+int roost_moe_tile_rows(void);   /* rows of a tile of sorted rows */
+/* scratch: int32[2 * tokens * top]; tiles: int32[3 * max_tiles], max_tiles >= ceil(tokens * top / tile rows) + experts. */
+int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
+                    int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, roost_stream_t stream);
+int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
+                           roost_stream_t stream);
+/* out[row, :] = a[row, :] w1[e]^T (w2 null) or silu(a w1[e]^T) * (a w2[e]^T), e the row's expert; w: [experts, n, k]. */
+int roost_moe_expert_gemm(const void* a, const void* w1, const void* w2, void* out, const int32_t* tiles, int max_tiles,
+                          const int32_t* expert_of, int rows, int n, int k, int form, int dtype, roost_stream_t stream);
+int roost_moe_combine(const void* ys, const int32_t* inverse, const void* shared, void* out, int tokens, int hidden, int top, int dtype,
+                      roost_stream_t stream);
 
 #ifdef __cplusplus
 }

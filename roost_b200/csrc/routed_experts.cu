@@ -1,0 +1,288 @@
+// A feed-forward routed over experts, on the device from the router's logits to the summed outputs.
+//
+//   route:        per token the `top` largest logits choose its experts (ties to the lower index; the sigmoid is monotonic, so the
+//                 logits are compared); a pair (token, choice) gets the weight sigmoid(logit). Pairs are sorted by expert:
+//                 offsets[e] .. offsets[e+1] are expert e's rows; token_of / weight_of / expert_of give a sorted row's token,
+//                 weight and expert; inverse[token * top + k] is where the token's k-th choice went. The sorted rows are also
+//                 cut into tiles of kMoeTile rows that meet one expert each: tiles[3n ..] = (expert, first row, one past the last).
+//   gather_scale: xs[row, :] = weight_of[row] * x[token_of[row], :], the product formed in 32-bit and rounded once.
+//   expert products over the sorted rows: out = silu(xs Wg[e]^T) * (xs Wu[e]^T), or out = act Wd[e]^T. Two forms: tiles of
+//                 rows on FFMA (every output sums over k in increasing order in one thread), and, for the few rows of a decode
+//                 step, a warp an output that streams the row's expert with 16-byte loads.
+//   combine:      out[t, :] = sum_k ys[inverse[t * top + k], :] (+ shared[t, :]), summed in 32-bit in the order of k.
+// One block does the routing: a step has at most a few thousand tokens and the work is a few comparisons each.
+#include "common.cuh"
+
+namespace roost {
+
+constexpr int kMoeTile = 64;
+constexpr int kMoeMaxTop = 32;
+
+__global__ void __launch_bounds__(1024) moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top,
+                                                        int32_t* __restrict__ token_of, float* __restrict__ weight_of,
+                                                        int32_t* __restrict__ expert_of, int32_t* __restrict__ inverse,
+                                                        int32_t* __restrict__ offsets, int32_t* __restrict__ tiles, int max_tiles,
+                                                        int32_t* __restrict__ pair_expert, int32_t* __restrict__ pair_rank) {
+  extern __shared__ int32_t counts[];      // [experts] counts, then [experts + 1] offsets
+  int32_t* offs = counts + experts;
+  pdl_launch_dependents();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  pdl_wait();
+  __syncthreads();
+  for (int t = threadIdx.x; t < tokens; t += blockDim.x) {
+    const float* z = logits + (size_t)t * experts;
+    int chosen[kMoeMaxTop];
+    for (int k = 0; k < top; ++k) {
+      int best = -1;
+      float bz = 0.f;
+      for (int e = 0; e < experts; ++e) {
+        bool taken = false;
+        for (int c = 0; c < k; ++c) taken |= chosen[c] == e;
+        const float v = z[e];
+        if (!taken && (best < 0 || v > bz)) {
+          best = e;
+          bz = v;
+        }
+      }
+      chosen[k] = best;
+      pair_expert[(size_t)t * top + k] = best;
+      pair_rank[(size_t)t * top + k] = atomicAdd(&counts[best], 1);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, n = 0;
+    for (int e = 0; e < experts; ++e) {
+      offs[e] = at;
+      offsets[e] = at;
+      for (int r = at; r < at + counts[e]; r += kMoeTile) {
+        tiles[3 * n] = e;
+        tiles[3 * n + 1] = r;
+        tiles[3 * n + 2] = min(r + kMoeTile, at + counts[e]);
+        ++n;
+      }
+      at += counts[e];
+    }
+    offs[experts] = at;
+    offsets[experts] = at;
+    for (; n < max_tiles; ++n) tiles[3 * n] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < tokens * top; i += blockDim.x) {
+    const int e = pair_expert[i];
+    const int dest = offs[e] + pair_rank[i];
+    const float z = logits[(size_t)(i / top) * experts + e];
+    token_of[dest] = i / top;
+    weight_of[dest] = 1.0f / (1.0f + expf(-z));
+    expert_of[dest] = e;
+    inverse[i] = dest;
+  }
+}
+
+template <typename T>
+__global__ void moe_gather_scale_kernel(const T* __restrict__ x, T* __restrict__ xs, const int32_t* __restrict__ token_of,
+                                        const float* __restrict__ weight_of, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = blockIdx.x;
+  const T* src = x + (size_t)token_of[row] * hidden;
+  const float w = weight_of[row];
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[(size_t)row * hidden + i] = from_float<T>(w * to_float(src[i]));
+}
+
+// Tiles of 64 sorted rows x 64 outputs of the tile's expert; k in steps of 16. GATED: two weights share the rows and the output
+// is silu(a Wg^T) * (a Wu^T).
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
+                                                           T* __restrict__ out, const int32_t* __restrict__ tiles, int N, int K) {
+  constexpr int BM = kMoeTile, BN = 64, BK = 16;
+  __shared__ float as[BK][BM + 1];
+  __shared__ float ws1[BK][BN + 1];
+  __shared__ float ws2[GATED ? BK : 1][BN + 1];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = tiles[3 * blockIdx.y];
+  if (e < 0) return;
+  const int m0 = tiles[3 * blockIdx.y + 1], m_end = tiles[3 * blockIdx.y + 2];
+  const int n0 = blockIdx.x * BN;
+  const T* wa = w1 + (size_t)e * N * K;
+  const T* wb = GATED ? w2 + (size_t)e * N * K : nullptr;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float acc1[4][4], acc2[GATED ? 4 : 1][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      acc1[i][j] = 0.f;
+      if (GATED) acc2[i][j] = 0.f;
+    }
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      const int row = idx >> 4, col = idx & 15;
+      const int k = k0 + col, m = m0 + row, n = n0 + row;
+      as[col][row] = (m < m_end && k < K) ? to_float(a[(size_t)m * K + k]) : 0.f;
+      ws1[col][row] = (n < N && k < K) ? to_float(wa[(size_t)n * K + k]) : 0.f;
+      if (GATED) ws2[col][row] = (n < N && k < K) ? to_float(wb[(size_t)n * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[4], bv[4], cv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = as[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        bv[j] = ws1[kk][tx * 4 + j];
+        if (GATED) cv[j] = ws2[kk][tx * 4 + j];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc1[i][j] = fmaf(av[i], bv[j], acc1[i][j]);
+          if (GATED) acc2[i][j] = fmaf(av[i], cv[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= m_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc1[i][j];
+      if (GATED) {
+        const float g = to_float(from_float<T>(v)), up = to_float(from_float<T>(acc2[i][j]));   // the two products, rounded as outputs
+        v = g / (1.0f + expf(-g)) * up;
+      }
+      out[(size_t)m * N + n] = from_float<T>(v);
+    }
+  }
+}
+
+// Few rows: a block per sorted row and 8 outputs, a warp an output; lanes stride over k.
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
+                                                          T* __restrict__ out, const int32_t* __restrict__ expert_of, int N, int K) {
+  constexpr int V = Vec<T>::N;
+  pdl_launch_dependents();
+  const int row = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y * 8 + warp;
+  pdl_wait();
+  if (n >= N) return;
+  const int e = expert_of[row];
+  const T* ar = a + (size_t)row * K;
+  const T* wr1 = w1 + ((size_t)e * N + n) * K;
+  const T* wr2 = GATED ? w2 + ((size_t)e * N + n) * K : nullptr;
+  float s1 = 0.f, s2 = 0.f;
+  if (K % V == 0 && ((uintptr_t)ar % 16 == 0) && ((uintptr_t)wr1 % 16 == 0) && (!GATED || (uintptr_t)wr2 % 16 == 0)) {
+    for (int k = lane * V; k < K; k += 32 * V) {
+      float av[V], bv[V];
+      Vec<T>::load(ar + k, av);
+      Vec<T>::load(wr1 + k, bv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) s1 = fmaf(av[i], bv[i], s1);
+      if (GATED) {
+        Vec<T>::load(wr2 + k, bv);
+#pragma unroll
+        for (int i = 0; i < V; ++i) s2 = fmaf(av[i], bv[i], s2);
+      }
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) {
+      const float av = to_float(ar[k]);
+      s1 = fmaf(av, to_float(wr1[k]), s1);
+      if (GATED) s2 = fmaf(av, to_float(wr2[k]), s2);
+    }
+  }
+  s1 = warp_sum(s1);
+  if (GATED) s2 = warp_sum(s2);
+  if (lane == 0) {
+    float v = s1;
+    if (GATED) {
+      const float g = to_float(from_float<T>(s1)), up = to_float(from_float<T>(s2));
+      v = g / (1.0f + expf(-g)) * up;
+    }
+    out[(size_t)row * N + n] = from_float<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ ys, const int32_t* __restrict__ inverse, const T* __restrict__ shared,
+                                   T* __restrict__ out, int hidden, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc += to_float(ys[(size_t)inverse[(size_t)t * top + k] * hidden + i]);
+    if (shared) acc += to_float(shared[(size_t)t * hidden + i]);
+    out[(size_t)t * hidden + i] = from_float<T>(acc);
+  }
+}
+
+}  // namespace roost
+
+using namespace roost;
+
+extern "C" int roost_moe_tile_rows(void) { return kMoeTile; }
+
+extern "C" int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
+                               int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts, "moe_route: sizes do not fit");
+  if (top > kMoeMaxTop || experts > 4096) return fail(ROOST_ERR_UNSUPPORTED, "moe_route: more than 32 choices a token or 4096 experts");
+  ROOST_REQUIRE((int64_t)max_tiles >= ((int64_t)tokens * top + kMoeTile - 1) / kMoeTile + experts, "moe_route: the tile list is too short");
+  if (tokens == 0) return ROOST_OK;
+  const size_t smem = ((size_t)2 * experts + 1) * sizeof(int32_t);
+  launch_kernel(moe_route_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, logits, tokens, experts, top, token_of, weight_of, expert_of,
+                inverse, offsets, tiles, max_tiles, scratch, scratch + (size_t)tokens * top);
+  return check_launch("moe_route");
+}
+
+extern "C" int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
+                                      roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && hidden > 0, "moe_gather_scale: sizes must be positive");
+  if (rows == 0) return ROOST_OK;
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(moe_gather_scale_kernel<T>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const T*)x, (T*)xs,
+                                               token_of, weight_of, hidden));
+  return check_launch("moe_gather_scale");
+}
+
+// form 0: tiles of rows (tiles: the route's list of max_tiles entries); form 1: a warp an output (expert_of: a sorted row's expert).
+extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* w2, void* out, const int32_t* tiles, int max_tiles,
+                                     const int32_t* expert_of, int rows, int n, int k, int form, int dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && n > 0 && k > 0 && (form == 0 || form == 1), "moe_expert_gemm: sizes do not fit");
+  if (rows == 0) return ROOST_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (form == 0) {
+    dim3 grid((n + 63) / 64, max_tiles);
+    if (max_tiles > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_expert_gemm: more than 65535 tiles of rows");
+    ROOST_DISPATCH_DTYPE(dtype, T, {
+      if (w2) launch_kernel(moe_tile_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k);
+      else launch_kernel(moe_tile_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k);
+    });
+  } else {
+    dim3 grid(rows, (n + 7) / 8);
+    if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_expert_gemm: too many outputs");
+    ROOST_DISPATCH_DTYPE(dtype, T, {
+      if (w2) launch_kernel(moe_row_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k);
+      else launch_kernel(moe_row_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k);
+    });
+  }
+  return check_launch("moe_expert_gemm");
+}
+
+extern "C" int roost_moe_combine(const void* ys, const int32_t* inverse, const void* shared, void* out, int tokens, int hidden, int top, int dtype,
+                                 roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && hidden > 0 && top > 0, "moe_combine: sizes must be positive");
+  if (tokens == 0) return ROOST_OK;
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(moe_combine_kernel<T>, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, (const T*)ys, inverse,
+                                               (const T*)shared, (T*)out, hidden, top));
+  return check_launch("moe_combine");
+}

@@ -7,13 +7,14 @@ no CUDA device is present, ``load()`` raises and nothing in the engine runs.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 
 import torch
 
 from . import build
 
-ABI_VERSION = 11
+ABI_VERSION = 12
 F32, BF16 = 0, 1
 
 
@@ -102,11 +103,52 @@ _SIGNATURES = {
     "roost_gemm_stream_swiglu_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_stream_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                  c_void_p],
+    "roost_embedding_scaled": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_softcap": [c_void_p, c_int64, c_float, c_void_p],
+    "roost_gemm_simt_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                c_int, c_int, c_void_p],
+    "roost_latent_prepare": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_float, c_int, c_void_p],
+    "roost_latent_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "roost_mamba2_conv": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                          c_int, c_int, c_int, c_void_p],
+    "roost_mamba2_conv_state": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_mamba2_scan": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_gated_group_norm": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_moe_tile_rows": [],
+    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "roost_moe_gather_scale": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_argmax_split": [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
 }
+
+
+@dataclass
+class MoeRoute:
+    """What ``moe_route`` leaves on the device: the (token, choice) pairs sorted by expert. ``token``/``weight``/``expert``:
+    a sorted row's token, weight and expert; ``inverse[token * top + k]``: where the token's k-th choice went; ``offsets``:
+    the experts' row ranges; ``tiles``: (expert, first row, one past the last) of every tile of sorted rows, -1 beyond.
+    ``form``: which expert product the step runs (0: tiles of rows, 1: a warp an output, for few rows)."""
+    top: int
+    rows: int
+    token: torch.Tensor
+    weight: torch.Tensor
+    expert: torch.Tensor
+    inverse: torch.Tensor
+    offsets: torch.Tensor
+    tiles: torch.Tensor
+    max_tiles: int
+    form: int
+
+
+MOE_ROW_FORM_MAX_ROWS = 64   # sorted rows up to which a bfloat16 step streams each row's expert instead of tiling the rows
 
 
 class KernelLibrary:
@@ -440,6 +482,183 @@ class KernelLibrary:
         out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
         self._call("roost_gemm_stream_swiglu", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
+        return out
+
+    # ------------------------------------------------------------------ a 32-bit stream's ends and norm
+    def embedding_scaled(self, table: torch.Tensor, ids: torch.Tensor, scale: float) -> torch.Tensor:
+        """table[ids] * scale as a float32 stream."""
+        _need(table, "table"); _need(ids, "ids", torch.int32)
+        T, (V, H) = ids.numel(), table.shape
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+        self._call("roost_embedding_scaled", _ptr(table), _ptr(ids), _ptr(out), T, H, V, scale, dtype_code(table.dtype), _stream())
+        return out
+
+    def layer_norm(self, stream: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                   addend: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+        """Layer norm of the float32 ``stream`` (plus ``addend``, added in 32-bit and written back unless ``rows`` gathers)
+        into ``out_dtype``."""
+        _need(stream, "stream", torch.float32); _need(w, "w", torch.float32); _need(b, "b", torch.float32)
+        H = stream.shape[-1]
+        if w.numel() != H or b.numel() != H:
+            raise KernelError(f"layer_norm: weight and bias must have {H} elements")
+        if addend is not None:
+            _need(addend, "addend", out_dtype)
+            if addend.shape != stream.shape:
+                raise KernelError("layer_norm: the addend and the stream differ in shape")
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+        n = stream.numel() // H if rows is None else rows.numel()
+        out = torch.empty((n, H), dtype=out_dtype, device=stream.device)
+        self._call("roost_layer_norm", _ptr(stream), _ptr(addend), _ptr(w), _ptr(b), _ptr(out), _ptr(rows), n, H, eps, dtype_code(out_dtype),
+                   _stream())
+        return out
+
+    def softcap_(self, logits: torch.Tensor, cap: float) -> torch.Tensor:
+        _need(logits, "logits", torch.float32)
+        self._call("roost_softcap", _ptr(logits), logits.numel(), cap, _stream())
+        return logits
+
+    def gemm_simt_batched(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """out[b] = a[b] w[b]^T on FFMA; a [B, M, K], w [B, N, K] and out [B, M, N] may be strided views with a dense last
+        dimension."""
+        B, M, K = a.shape
+        _, N, _ = w.shape
+        if w.shape != (B, N, K) or out.shape != (B, M, N) or a.dtype != w.dtype:
+            raise KernelError(f"gemm_simt_batched: shapes {tuple(a.shape)}, {tuple(w.shape)}, {tuple(out.shape)} do not fit")
+        for n, t in (("a", a), ("w", w), ("out", out)):
+            if not t.is_cuda or t.stride(2) != 1:
+                raise KernelError(f"gemm_simt_batched: {n} must be on the device with a dense last dimension")
+        self._call("roost_gemm_simt_batched", _ptr(a), _ptr(w), _ptr(out), B, M, N, K, a.stride(1), w.stride(1), out.stride(1), a.stride(0),
+                   w.stride(0), out.stride(0), dtype_code(a.dtype), dtype_code(out.dtype), _stream())
+        return out
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prepare(self, q, down, pool, latent_w, inv_freq, rotary_dim, positions, slot_mapping, heads, nope, rope, rank, eps, page_size) -> None:
+        """Rotates the heads' rotated query parts in place and, when ``down`` is given, writes the tokens' cache entries."""
+        _need(q, "q"); _need(inv_freq, "inv_freq", torch.float64); _need(positions, "positions", torch.int32)
+        T = q.shape[0]
+        if q.shape[1] != heads * (nope + rope) or inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("latent_prepare: q or inv_freq do not fit the sizes")
+        if down is not None:
+            _need(down, "down", q.dtype); _need(pool, "pool", q.dtype); _need(latent_w, "latent_w", torch.float32)
+            _need(slot_mapping, "slot_mapping", torch.int32)
+            if tuple(down.shape) != (T, rank + rope) or tuple(pool.shape[1:]) != (1, page_size, rank + rope) or latent_w.numel() != rank:
+                raise KernelError("latent_prepare: down, pool or the latent's weight do not fit the sizes")
+        self._call("roost_latent_prepare", _ptr(q), _ptr(down), _ptr(pool), _ptr(latent_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping),
+                   T, heads, nope, rope, rotary_dim, rank, eps, dtype_code(q.dtype), _stream())
+
+    def latent_splits_for(self, tokens: int, heads: int, window: int | None, kv_cap: int) -> int:
+        """Blocks a token's keys are dealt to: 1 when the step's (token, 8 heads) blocks fill the device by themselves, else as
+        many as give two blocks an SM, up to the tiles a token can have (from the window and the bound on the requests'
+        lengths, so that every replay of a captured step agrees) and to 32."""
+        if not self._decode_ctas:
+            self._decode_ctas = 2 * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        blocks = tokens * (-(-heads // 8))
+        reach = min(window, kv_cap) if window else kv_cap
+        tiles = -(-max(reach, 1) // 32) + 1
+        return max(1, min(self._decode_ctas // max(blocks, 1), tiles, 32))
+
+    def latent_attention(self, q_latent, q, pool, positions, token_row, kv_indptr, kv_indices, heads, nope, rope, rank, scale, window,
+                         kv_cap: int = 0, few_rows: bool = False) -> torch.Tensor:
+        _need(q_latent, "q_latent"); _need(q, "q", q_latent.dtype); _need(pool, "pool", q.dtype)
+        for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
+            _need(t, n, torch.int32)
+        T = q.shape[0]
+        if tuple(q_latent.shape) != (heads, T, rank) or pool.shape[-1] != rank + rope or pool.shape[1] != 1:
+            raise KernelError("latent_attention: q_latent or the pool do not fit the sizes")
+        out = torch.empty((heads, T, rank), dtype=q.dtype, device=q.device)
+        splits = self.latent_splits_for(T, heads, window, kv_cap) if kv_cap else 1
+        part = torch.empty((T * heads * splits * (rank + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
+        self._call("roost_latent_attention", _ptr(q_latent), _ptr(q), _ptr(out), _ptr(part), _ptr(pool), _ptr(positions), _ptr(token_row),
+                   _ptr(kv_indptr), _ptr(kv_indices), T, heads, nope, rope, rank, pool.shape[2], scale, int(window) if window else 0, splits,
+                   dtype_code(q.dtype), _stream(), launches=2 if splits > 1 else 1)
+        return out
+
+    # ------------------------------------------------------------------ the Mamba-2 recurrence
+    def mamba2_conv(self, u, col, channels, w, b, state, conv_off, token_row, q_indptr, slots) -> torch.Tensor:
+        _need(u, "u"); _need(w, "w", torch.float32); _need(b, "b", torch.float32); _need(state, "state", torch.float32)
+        T = u.shape[0]
+        out = torch.empty((T, channels), dtype=u.dtype, device=u.device)
+        self._call("roost_mamba2_conv", _ptr(u), u.stride(0), col, _ptr(out), _ptr(w), _ptr(b), _ptr(state), state.stride(0), conv_off,
+                   _ptr(token_row), _ptr(q_indptr), _ptr(slots), T, channels, w.shape[1], dtype_code(u.dtype), _stream())
+        return out
+
+    def mamba2_conv_state(self, u, col, channels, taps, state, conv_off, q_indptr, slots) -> None:
+        _need(u, "u"); _need(state, "state", torch.float32)
+        self._call("roost_mamba2_conv_state", _ptr(u), u.stride(0), col, _ptr(state), state.stride(0), conv_off, _ptr(q_indptr), _ptr(slots),
+                   slots.numel(), channels, taps, dtype_code(u.dtype), _stream(), launches=1 if taps > 1 else 0)
+
+    def mamba2_scan(self, xbc, u, dt_col, dt_bias, a_log, d, state, q_indptr, slots, heads, head_dim, state_rows, groups) -> torch.Tensor:
+        _need(xbc, "xbc"); _need(u, "u", xbc.dtype); _need(state, "state", torch.float32)
+        for n, t in (("dt_bias", dt_bias), ("A_log", a_log), ("D", d)):
+            _need(t, n, torch.float32)
+        T = xbc.shape[0]
+        y = torch.empty((T, heads * head_dim), dtype=torch.float32, device=xbc.device)
+        self._call("roost_mamba2_scan", _ptr(xbc), _ptr(u), u.stride(0), dt_col, _ptr(y), _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(state),
+                   state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), heads, head_dim, state_rows, groups, dtype_code(xbc.dtype),
+                   _stream())
+        return y
+
+    def gated_group_norm(self, y, u, w, groups, eps, out_dtype) -> torch.Tensor:
+        _need(y, "y", torch.float32); _need(u, "u", out_dtype); _need(w, "w", torch.float32)
+        T, inner = y.shape
+        out = torch.empty((T, inner), dtype=out_dtype, device=y.device)
+        self._call("roost_gated_group_norm", _ptr(y), _ptr(u), u.stride(0), _ptr(w), _ptr(out), T, inner, groups, eps, dtype_code(out_dtype),
+                   _stream())
+        return out
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, logits: torch.Tensor, top: int) -> MoeRoute:
+        _need(logits, "logits", torch.float32)
+        T, E = logits.shape
+        rows = T * top
+        tile = self._lib.roost_moe_tile_rows()
+        max_tiles = -(-rows // tile) + E
+        dev = logits.device
+        ints = torch.empty((4 * rows + (E + 1) + 3 * max_tiles + 2 * rows,), dtype=torch.int32, device=dev)
+        token, expert, inverse = ints[:rows], ints[rows : 2 * rows], ints[2 * rows : 3 * rows]
+        at = 3 * rows
+        offsets, at = ints[at : at + E + 1], at + E + 1
+        tiles, at = ints[at : at + 3 * max_tiles], at + 3 * max_tiles
+        scratch = ints[at : at + 2 * rows]
+        weight = torch.empty((rows,), dtype=torch.float32, device=dev)
+        self._call("roost_moe_route", _ptr(logits), T, E, top, _ptr(token), _ptr(weight), _ptr(expert), _ptr(inverse), _ptr(offsets), _ptr(tiles),
+                   max_tiles, _ptr(scratch), _stream())
+        return MoeRoute(top=top, rows=rows, token=token, weight=weight, expert=expert, inverse=inverse, offsets=offsets, tiles=tiles,
+                        max_tiles=max_tiles, form=0)
+
+    def moe_gather_scale(self, x: torch.Tensor, route: MoeRoute) -> torch.Tensor:
+        _need(x, "x")
+        xs = torch.empty((route.rows, x.shape[1]), dtype=x.dtype, device=x.device)
+        self._call("roost_moe_gather_scale", _ptr(x), _ptr(xs), _ptr(route.token), _ptr(route.weight), route.rows, x.shape[1], dtype_code(x.dtype),
+                   _stream())
+        return xs
+
+    def _moe_gemm(self, a, w1, w2, route: MoeRoute) -> torch.Tensor:
+        _need(a, "a"); _need(w1, "w1", a.dtype)
+        E, N, K = w1.shape
+        if a.shape != (route.rows, K) or (w2 is not None and w2.shape != w1.shape):
+            raise KernelError(f"moe_expert_gemm: rows {tuple(a.shape)} against weights {tuple(w1.shape)}")
+        form = 1 if (a.dtype == torch.bfloat16 and route.rows <= MOE_ROW_FORM_MAX_ROWS) else 0
+        out = torch.empty((route.rows, N), dtype=a.dtype, device=a.device)
+        self._call("roost_moe_expert_gemm", _ptr(a), _ptr(w1), _ptr(w2), _ptr(out), _ptr(route.tiles), route.max_tiles, _ptr(route.expert),
+                   route.rows, N, K, form, dtype_code(a.dtype), _stream())
+        return out
+
+    def moe_expert_gate_up(self, xs, gate, up, route: MoeRoute) -> torch.Tensor:
+        """silu(xs Wg[e]^T) * (xs Wu[e]^T) over the sorted rows, e the row's expert."""
+        return self._moe_gemm(xs, gate, up, route)
+
+    def moe_expert_down(self, act, down, route: MoeRoute) -> torch.Tensor:
+        return self._moe_gemm(act, down, None, route)
+
+    def moe_combine(self, ys: torch.Tensor, route: MoeRoute, shared: torch.Tensor | None = None) -> torch.Tensor:
+        _need(ys, "ys")
+        T, H = route.rows // route.top, ys.shape[1]
+        if shared is not None:
+            _need(shared, "shared", ys.dtype)
+        out = torch.empty((T, H), dtype=ys.dtype, device=ys.device)
+        self._call("roost_moe_combine", _ptr(ys), _ptr(route.inverse), _ptr(shared), _ptr(out), T, H, route.top, dtype_code(ys.dtype), _stream())
         return out
 
     def attention_set_decode_tma(self, on: bool) -> None:

@@ -35,6 +35,8 @@ class Mamba2(Mixer):
             raise ValueError(f"mamba2: {self.inner} inner values do not divide into {s.norm_groups} norm groups")
         if s.state > 256:
             raise ValueError(f"mamba2: a state of {s.state} rows is beyond 256, the largest the scan kernel keeps in registers")
+        if s.head_dim > 128:
+            raise ValueError(f"mamba2: heads of {s.head_dim} values are beyond 128, the most a block of the scan kernel holds")
         if s.conv_taps > 16:
             raise ValueError(f"mamba2: {s.conv_taps} taps are beyond 16, the most the convolution kernel serves")
         self.spec = s

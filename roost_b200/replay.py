@@ -12,7 +12,7 @@ import sys
 from pathlib import Path
 
 REPLAY_PAGE_SIZE = 16   # divides 64, the granule --max-tokens is counted in
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 4    # state slots: a replayed schedule keeps at most this many requests live
 
 
 def main(argv=None) -> int:
