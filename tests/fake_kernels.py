@@ -219,7 +219,7 @@ class FakeKernels:
         s = torch.sigmoid(logits)
         pairs = []
         for t in range(T):
-            for e in sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]:
+            for e in sorted(range(E), key=lambda e: (-float(logits[t, e]), e))[:top]:     # by logit: the sigmoid saturates in 32-bit
                 pairs.append((e, t, float(s[t, e])))
         order = sorted(range(len(pairs)), key=lambda i: (pairs[i][0], i))
         inverse = torch.zeros(len(pairs), dtype=torch.int32)

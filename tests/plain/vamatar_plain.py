@@ -143,15 +143,23 @@ def gated_ff(x, w, prefix):
     return (silu(x @ w[prefix + "gate"].T) * (x @ w[prefix + "up"].T)) @ w[prefix + "down"].T
 
 
-def routed_ff(x, w, prefix, f, round_input=None):
+def routed_ff(x, w, prefix, f, round_input=None, forced=None, slack=0.0):
     """Scores sigmoid(W_router x); the ``top`` largest choose the experts; each chosen expert is given score * x and the
     outputs are summed; a shared expert, when the layer has one, sees x itself. ``round_input``: what the engine under
-    test does to an expert's scaled input (rounding to bfloat16), None for nothing."""
+    test does to an expert's scaled input (rounding to bfloat16), None for nothing. ``forced`` [T, top]: the experts an
+    engine chose; they are used instead of this function's own choice after a check that each one's router logit is
+    within ``slack`` of the ``top``-th largest (an engine in lower precision may order near-equal scores differently)."""
     E, top = f["router"]["experts"], f["router"]["top"]
-    s = torch.sigmoid(x @ w[prefix + "router"].T)
+    z = x @ w[prefix + "router"].T
+    s = torch.sigmoid(z)
     out = torch.zeros_like(x)
     for t in range(x.shape[0]):
         order = sorted(range(E), key=lambda e: (-float(s[t, e]), e))[:top]
+        if forced is not None:
+            mine, order = order, [int(e) for e in forced[t]]
+            assert len(set(order)) == top, f"token {t}: the engine chose {order}"
+            for e in order:
+                assert float(z[t, e]) >= float(z[t, mine[-1]]) - slack, f"token {t}: the engine chose expert {e}, logit {float(z[t, e])}, but the {top}-th largest is {float(z[t, mine[-1]])}"
         for e in order:
             xin = (s[t, e] * x[t])[None, :]
             if round_input is not None:
@@ -163,8 +171,9 @@ def routed_ff(x, w, prefix, f, round_input=None):
 
 
 # ---------------------------------------------------------------------------------------------- the model
-def forward(cfg, w, ids, return_layers: bool = False, round_input=None):
-    """Logits [T, vocab] of one sequence at positions 0..T-1 (and the stream after every layer when asked)."""
+def forward(cfg, w, ids, return_layers: bool = False, round_input=None, forced=None, slack=0.0):
+    """Logits [T, vocab] of one sequence at positions 0..T-1 (and the stream after every layer when asked). ``forced``:
+    {layer index: [T, top] experts} for routed layers whose choices are given (see ``routed_ff``)."""
     eps = cfg["norm"]["eps"]
     positions = list(range(len(ids)))
     h = w["embed"][torch.as_tensor(ids, dtype=torch.long)] * cfg["embedding"]["scale"]
@@ -188,7 +197,7 @@ def forward(cfg, w, ids, return_layers: bool = False, round_input=None):
             if f["kind"] == "dense":
                 h = h + gated_ff(x, w, p + "mlp.")
             elif f["kind"] == "moe":
-                h = h + routed_ff(x, w, p + "mlp.", f, round_input)
+                h = h + routed_ff(x, w, p + "mlp.", f, round_input, None if forced is None else forced.get(i), slack)
             else:
                 raise ValueError(f"layer {i}: no feed-forward '{f['kind']}'")
         layers.append(h)

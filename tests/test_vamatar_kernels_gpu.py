@@ -1,0 +1,184 @@
+"""The kernels of the Vamatar parts on the device, each against the plain formula, and the forms a step chooses between
+against one another (split keys against one block a token, a warp an output against tiles of rows); sizes of every
+register class of the scan kernel; the replay tool on a Vamatar folder."""
+import json
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from roost_b200.engine.executor import StepEntry, StepExecutor
+from tests import helpers as H
+from tests import vamatar_models as VM
+from tests.conftest import ROOT
+from tests.plain import vamatar_plain as P
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def close(got, want, dtype, what, f32=2e-5, bf16=2e-2):
+    err = H.scaled_error(got.float(), want)
+    print(f"MEASURED {what} {dtype}: {err:.3e}")
+    assert err < (f32 if dtype == torch.float32 else bf16), (what, err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [20, 320, 4096])
+def test_layer_norm_over_a_32_bit_stream(kernels, dtype, hidden):
+    g = torch.Generator().manual_seed(hidden)
+    stream = (torch.randn(9, hidden, generator=g) * 3 + 1).cuda()
+    addend = torch.randn(9, hidden, generator=g).to(dtype).cuda()
+    w, b = torch.randn(hidden, generator=g).cuda(), torch.randn(hidden, generator=g).cuda()
+    want_sum = stream.double().cpu() + addend.double().cpu()
+    want = P.layer_norm(want_sum, w.double().cpu(), b.double().cpu(), 1e-5)
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32).cuda()
+    before = stream.clone()
+    gathered = kernels.layer_norm(stream, w, b, 1e-5, dtype, addend, rows)
+    assert torch.equal(stream, before)                  # gathered rows leave the stream as it is
+    close(gathered, want[[7, 0, 3]], dtype, "layer norm of gathered rows")
+    out = kernels.layer_norm(stream, w, b, 1e-5, dtype, addend)
+    close(out, want, dtype, "add + layer norm")
+    assert H.scaled_error(stream, want_sum) < 1e-6      # the stream holds the 32-bit sum, not a rounded one
+    close(kernels.layer_norm(stream, w, b, 1e-5, dtype), want, dtype, "layer norm alone")
+
+
+def test_scaled_embedding_and_capped_logits(kernels):
+    table = torch.randn(30, 24).to(torch.bfloat16).cuda()
+    ids = torch.tensor([3, 29, 0, 3], dtype=torch.int32).cuda()
+    out = kernels.embedding_scaled(table, ids, 0.3)
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), table.float().cpu()[ids.long().cpu()] * torch.tensor(0.3))
+    z = (torch.randn(5, 77) * 30).cuda()
+    want = 12.0 * torch.tanh(z.double().cpu() / 12.0)
+    assert H.scaled_error(kernels.softcap_(z.clone(), 12.0), want) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 37])
+def test_latent_attention_with_split_keys_against_the_plain_sum(kernels, dtype, window):
+    """Three rows of unequal length, one token each at the end of 5, 130 and 260 cached entries on pages of 8 handed out in
+    a scrambled order; the keys of a token dealt to several blocks (a decode step of few rows) and to one."""
+    heads, nope, rope, rank, page = 5, 8, 6, 20, 8
+    g = torch.Generator().manual_seed(3)
+    lens = [5, 130, 260]
+    n_pages = sum(-(-n // page) for n in lens)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    pool = torch.zeros(n_pages, 1, page, rank + rope)
+    entries, tables = [], []
+    for n in lens:
+        e = torch.randn(n, rank + rope, generator=g)
+        mine = [order.pop() for _ in range(-(-n // page))]
+        for j in range(n):
+            pool[mine[j // page], 0, j % page] = e[j]
+        entries.append(e)
+        tables.append(mine)
+    pool = pool.to(dtype).cuda()
+    T = len(lens)
+    q_latent = torch.randn(heads, T, rank, generator=g).to(dtype).cuda()
+    q = torch.randn(T, heads * (nope + rope), generator=g).to(dtype).cuda()
+    positions = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    token_row = torch.arange(T, dtype=torch.int32).cuda()
+    indptr = torch.tensor([0] + list(np.cumsum([len(t) for t in tables])), dtype=torch.int32).cuda()
+    indices = torch.tensor([p for t in tables for p in t], dtype=torch.int32).cuda()
+    scale = 0.21
+    want = torch.zeros(heads, T, rank, dtype=torch.float64)
+    for t, n in enumerate(lens):
+        lo = 0 if window is None else max(0, n - window)
+        e = pool[:, 0].reshape(-1, rank + rope).double().cpu()
+        rows = torch.stack([e[tables[t][j // page] * page + j % page] for j in range(lo, n)])
+        qr = q[t].double().cpu().reshape(heads, nope + rope)[:, nope:]
+        s = (q_latent[:, t].double().cpu() @ rows[:, :rank].T + qr @ rows[:, rank:].T) * scale
+        want[:, t] = torch.softmax(s, -1) @ rows[:, :rank]
+    args = (q_latent, q, pool, positions, token_row, indptr, indices, heads, nope, rope, rank, scale, window)
+    one = kernels.latent_attention(*args, 0)
+    split = kernels.latent_attention(*args, 1024, True)
+    assert kernels.latent_splits_for(T, heads, window, 1024) > 1
+    close(one, want, dtype, "latent attention, one block a token", bf16=1e-2)
+    close(split, want, dtype, "latent attention, split keys", bf16=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_routing_chooses_the_largest_scores_and_sorts_the_pairs_by_expert(kernels, dtype):
+    T, E, top, hidden, ff = 50, 9, 3, 24, 16
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(T, E, generator=g) * 3
+    logits[4, 2] = logits[4, 6] = logits[4].max() + 1          # a tie goes to the lower index
+    route = kernels.moe_route(logits.cuda(), top)
+    token, expert, weight, inverse = route.token.cpu(), route.expert.cpu(), route.weight.cpu(), route.inverse.cpu().long()
+    assert torch.equal(expert, expert.sort().values)            # sorted by expert
+    offsets = route.offsets.cpu()
+    assert int(offsets[-1]) == T * top and all(int((expert == e).sum()) == int(offsets[e + 1] - offsets[e]) for e in range(E))
+    for t in range(T):
+        want = sorted(range(E), key=lambda e: (-float(logits[t, e]), e))[:top]
+        assert [int(expert[inverse[t * top + k]]) for k in range(top)] == want
+        assert all(int(token[inverse[t * top + k]]) == t for k in range(top))
+        for k, e in enumerate(want):
+            assert abs(float(weight[inverse[t * top + k]]) - float(torch.sigmoid(logits[t, e].double()))) < 1e-6
+    tiles = route.tiles.cpu().reshape(-1, 3)
+    covered = sorted((int(a), int(b)) for e, a, b in tiles if e >= 0)
+    assert covered[0][0] == 0 and covered[-1][1] == T * top and all(x[1] == y[0] for x, y in zip(covered, covered[1:]))
+    # the expert products in both forms, and the sum
+    x = torch.randn(T, hidden, generator=g).to(dtype).cuda()
+    wg, wu = (torch.randn(E, ff, hidden, generator=g) * 0.3).to(dtype).cuda(), (torch.randn(E, ff, hidden, generator=g) * 0.3).to(dtype).cuda()
+    wd = (torch.randn(E, hidden, ff, generator=g) * 0.3).to(dtype).cuda()
+    shared = torch.randn(T, hidden, generator=g).to(dtype).cuda()
+    xs = kernels.moe_gather_scale(x, route)
+    outs = []
+    for form in (0, 1):
+        a = torch.empty(T * top, ff, dtype=dtype, device="cuda")
+        kernels._call("roost_moe_expert_gemm", xs.data_ptr(), wg.data_ptr(), wu.data_ptr(), a.data_ptr(), route.tiles.data_ptr(), route.max_tiles,
+                      route.expert.data_ptr(), T * top, ff, hidden, form, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
+        y = torch.empty(T * top, hidden, dtype=dtype, device="cuda")
+        kernels._call("roost_moe_expert_gemm", a.data_ptr(), wd.data_ptr(), None, y.data_ptr(), route.tiles.data_ptr(), route.max_tiles,
+                      route.expert.data_ptr(), T * top, hidden, ff, form, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
+        outs.append(kernels.moe_combine(y, route, shared))
+    want = shared.double().cpu().clone()
+    xd = x.double().cpu()
+    for t in range(T):
+        for e in sorted(range(E), key=lambda e: (-float(logits[t, e]), e))[:top]:
+            xin = (torch.sigmoid(logits[t, e].double()) * xd[t])[None]
+            w = {"gate": wg[e].double().cpu(), "up": wu[e].double().cpu(), "down": wd[e].double().cpu()}
+            want[t] += P.gated_ff(xin, w, "")[0]
+    close(outs[0], want, dtype, "experts on tiles of rows", bf16=4e-2)
+    close(outs[1], want, dtype, "experts, a warp an output", bf16=4e-2)
+
+
+@pytest.mark.parametrize("state,vdim", [(100, 24), (200, 40), (3, 128)])
+def test_the_recurrence_at_sizes_of_every_register_class(tmp_path, state, vdim):
+    cfg = VM.config([(VM.mamba(heads=2, vdim=vdim, state=state, groups=2, conv=4, norm_groups=1), None)], width=48, vocab=31, cap=None)
+    tensors = VM.draw_tensors(cfg, state)
+    folder = VM.write_model(tmp_path, cfg, tensors)
+    model = H.make_model(folder, torch.float32, "gpu")
+    ex = StepExecutor(model, page_size=4, num_pages=8, max_requests=2)
+    ids = H.random_ids(45, cfg["vocab"], 1)
+    got = torch.cat([ex.step([StepEntry("r", ids[:20], list(range(20)))]), ex.step([StepEntry("r", ids[20:22], [0, 1])])] +
+                    [ex.step([StepEntry("r", [t], [0])]) for t in ids[22:]])
+    want = P.forward(cfg, VM.plain_weights(tensors), ids)
+    assert H.scaled_error(got, want) < 2e-4 and H.rms_error(got, want) < 3e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_tool_on_a_vamatar_folder(tmp_path, dtype):
+    cfg = VM.WIDE
+    tensors = VM.draw_tensors(cfg, 8)
+    folder = VM.write_model(tmp_path / "model", cfg, tensors)
+    a, b = H.random_ids(70, cfg["vocab"], 1), H.random_ids(41, cfg["vocab"], 2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 32]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[:2], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[33:69], "want": [35]}, {"id": "b", "tokens": b[2:], "want": [38]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [line for line in r.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    assert not (out / "1.f32").exists()
+    read = lambda n, rows: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(rows, cfg["vocab"]))
+    w = VM.plain_weights(tensors)
+    wa, wb = P.forward(cfg, w, a), P.forward(cfg, w, b)
+    bound = 2e-4 if dtype == "float32" else 0.25
+    assert H.scaled_error(read(0, 2), wa[[0, 32]]) < bound
+    assert H.scaled_error(read(2, 2), torch.stack([wa[68], wb[40]])) < bound
+    assert H.scaled_error(read(3, 1), wa[69:70]) < bound
