@@ -333,6 +333,85 @@ def serving_main(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- the Vamatar design beside Qwen3
+# Layer sizes that resemble models of this kind (no released model's own): a latent attention with a 512- or 256-number latent
+# under a window, Mamba-2 blocks with a state of 128, routed experts with a shared one. The Qwen3-shaped model beside each has
+# the same width, number of layers and vocabulary, as many query heads, and the feed-forward rows a Vamatar token uses.
+def _vamatar_config(width, heads, dim, rot, vdim, rank, window, m_heads, m_vdim, state, groups, experts, top, ff, shared, dense_ff, layers, vocab):
+    latent = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "mask": {"size": window},
+              "rot": {"base": 1000000.0, "dims": rot}, "scale": (dim + rot) ** -0.5}
+    mamba = {"type": "mamba2", "mixer": {"heads": m_heads, "vdim": m_vdim, "state": state, "groups": groups, "conv": 4, "norm_groups": groups}}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff}, "shared": {"ff": shared}}
+    out, owner = [], None
+    for i in range(layers):       # of every four layers: latent attention (its own latent, then reading the last one's), then three recurrences
+        if i % 4 == 0:
+            mixer = dict(latent) if (i // 4) % 2 == 0 else dict(latent, kv_from=owner)
+            owner = i if (i // 4) % 2 == 0 else owner
+            out.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": dense_ff} if i == 0 else moe})
+        else:
+            out.append(dict(mamba, mlp=moe))
+    return {"architecture": "Vamatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "logit_softcap": 30.0, "layers": out}
+
+
+DESIGN_SIZES = {
+    "w1024": dict(width=1024, heads=16, dim=64, rot=32, vdim=64, rank=256, window=1024, m_heads=32, m_vdim=64, state=128, groups=1,
+                  experts=32, top=4, ff=512, shared=1024, dense_ff=3072, layers=8, vocab=32768),
+    "w2048": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, window=2048, m_heads=64, m_vdim=64, state=128, groups=8,
+                  experts=64, top=6, ff=768, shared=1536, dense_ff=6144, layers=8, vocab=65536),
+}
+
+
+def build_vamatar(sizes: dict, dtype, seed: int = 0):
+    import torch
+
+    from roost_b200.config.vamatar import VamatarConfig
+    from roost_b200.engine.model import Model
+    from roost_b200.kernels import library
+    from roost_b200.parts import Runtime
+    from roost_b200.weights.random_init import random_parameters
+    cfg = _vamatar_config(**sizes)
+    spec = VamatarConfig.from_dict(cfg).to_spec()
+    model = Model(spec, Runtime(dtype, "cuda", library.load()))
+    model.load(random_parameters(spec, seed, torch.device("cuda"), dtype, std=0.02))
+    return model, cfg
+
+
+def designs_main(args) -> int:
+    """Prefill and decode throughput of Vamatar models beside Qwen3-shaped models of equal size, one JSON line."""
+    import torch
+    pk, pk_src = peaks()
+    out = {}
+    for name in args.design_sizes.split(","):
+        s = DESIGN_SIZES[name]
+        rec = {}
+        for which in ("vamatar", "qwen3"):
+            if which == "vamatar":
+                model, _ = build_vamatar(s, torch.bfloat16)
+            else:
+                model, _ = build_model(s["layers"], torch.bfloat16, sizes=dict(
+                    QWEN3_8B, hidden_size=s["width"], num_attention_heads=s["heads"], num_key_value_heads=max(1, s["heads"] // 4),
+                    head_dim=s["dim"] + s["rot"] if s["dim"] + s["rot"] in (64, 128) else 128, intermediate_size=s["top"] * s["ff"] + s["shared"],
+                    vocab_size=s["vocab"]))
+            r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            ms = timed_prefill(model, args.prefill_tokens)
+            r["prefill"] = {"tokens": args.prefill_tokens, "ms": round(ms, 3), "tokens_per_s": round(args.prefill_tokens / ms * 1e3)}
+            for batch in _ints(args.design_batches):
+                tps, ms, launches, _ = timed_decode(model, batch, args.design_context, args.steps, max(args.warmup, 3))
+                r[f"decode_b{batch}"] = {"context": args.design_context, "ms": round(ms, 4), "tokens_per_s": round(tps), "launches": launches[0] // args.steps,
+                                         "library_launches": launches[1] // args.steps}
+            rec[which] = r
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        rec["config"] = s
+        out[name] = rec
+    print(json.dumps({"metric": "prefill and decode tokens/s of Vamatar models beside Qwen3-shaped models of equal width, depth and vocabulary",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "impl": "ours", "peaks": pk_src,
+                      "data": "synthetic: seeded random weights, seeded random tokens; device-timed with CUDA events", "sizes": out}))
+    return 0
+
+
 def reference_arm() -> int:
     print(json.dumps({"impl": "reference", "unavailable": "starlinghq/roost is a C#/.NET 10 program with no Python package "
                       "(pip install of the reference's source tree finds no setup.py or pyproject.toml) and no .NET SDK or runtime is on this image"}))
@@ -348,8 +427,12 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="layers built (default: all the layers of --sizes)")
     ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="whose layer sizes: Qwen3-0.6B, -8B (the headline) or -32B")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
-                    help="decode: the headline line; serving: concurrent requests with chunked prefill mixed with decoding")
+    ap.add_argument("--design-sizes", default="w1024,w2048", help="--workload designs: which of the Vamatar layer sizes to measure")
+    ap.add_argument("--design-batches", default="1,8", help="--workload designs: decode batch sizes")
+    ap.add_argument("--design-context", type=int, default=1024, help="--workload designs: keys every decoding request holds")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving", "designs"],
+                    help="decode: the headline line; serving: concurrent requests with chunked prefill mixed with decoding; "
+                         "designs: Vamatar models beside Qwen3-shaped models of equal size")
     ap.add_argument("--requests", type=int, default=32)
     ap.add_argument("--budget", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=256)
@@ -373,6 +456,8 @@ def main() -> int:
     warmup = max(args.warmup, 3)
     if args.workload == "serving":
         return serving_main(args)
+    if args.workload == "designs":
+        return designs_main(args)
 
     import torch
     pk, pk_kind = peaks()

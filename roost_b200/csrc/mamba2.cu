@@ -138,6 +138,131 @@ __global__ void mamba2_scan_kernel(const T* __restrict__ xbc, const T* __restric
   }
 }
 
+// The same walk for sizes of whole 16-byte vectors (state, head size, channel offsets), which is every model of real size:
+// a block takes 16 values of a head (64 threads), thread (p, s) keeps the s-th quarter of S[.][p], a contiguous run of
+// state indices, so B and C are read from shared memory 16 bytes at a time; the next 8 tokens' B, C and x arrive by
+// cp.async in the activation dtype while the current 8 are walked, and are widened when read.
+constexpr int kScanVecP = 16;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+template <typename T, int NI>
+__global__ void __launch_bounds__(64) mamba2_scan_vec_kernel(const T* __restrict__ xbc, const T* __restrict__ u, int64_t ld_u, int dt_col,
+                                                            float* __restrict__ y, const float* __restrict__ dt_bias,
+                                                            const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state,
+                                                            int64_t state_stride, const int32_t* __restrict__ q_indptr,
+                                                            const int32_t* __restrict__ slots, int heads, int P, int N, int groups) {
+  constexpr int V = Vec<T>::N;                    // elements of a 16-byte piece
+  constexpr int PAD = V;                          // a quarter's run is followed by one piece: the quarters fall in different banks
+  constexpr int ROW = kScanSlices * (NI + PAD);   // elements of a token's B (or C) in shared memory
+  __shared__ __align__(16) T sB[2][kScanChunk][ROW];
+  __shared__ __align__(16) T sC[2][kScanChunk][ROW];
+  __shared__ __align__(16) T sx[2][kScanChunk][kScanVecP];
+  __shared__ float sdt[2][2][kScanChunk];
+  pdl_launch_dependents();
+  const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * kScanVecP;
+  const int g = h / (heads / groups);
+  const int inner = heads * P, channels = inner + 2 * groups * N;
+  const int tid = threadIdx.x;
+  const int pl = tid / kScanSlices, s = tid % kScanSlices;     // the thread's value within the block, and its quarter
+  const int p = p0 + pl;
+  const bool live = p < P;
+  const int start = q_indptr[r], end = q_indptr[r + 1];
+  const float bias = dt_bias[h], rate = -expf(a_log[h]), skip = d_skip[h];
+  float* Sg = state + (size_t)slots[r] * state_stride + ((size_t)h * P + (live ? p : 0)) * N;
+  // pieces beyond the state's rows stay zero for the whole walk
+  for (int i = tid; i < 2 * kScanChunk * ROW; i += 64) {
+    (&sB[0][0][0])[i] = from_float<T>(0.f);
+    (&sC[0][0][0])[i] = from_float<T>(0.f);
+  }
+  pdl_wait();
+  if (end <= start) return;
+  float S[NI];
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int n = s * NI + i;
+    S[i] = (live && n < N) ? Sg[n] : 0.f;
+  }
+  __syncthreads();
+  const int pieces_n = N / V;                      // pieces of a token's B
+  const int pieces_x = kScanVecP / V;
+  auto issue = [&](int t0, int buf) {
+    const int nt = min(kScanChunk, end - t0);
+    for (int idx = tid; idx < nt * pieces_n; idx += 64) {
+      const int tt = idx / pieces_n, j = idx % pieces_n;
+      const int n = j * V;
+      const T* row = xbc + (size_t)(t0 + tt) * channels + inner + (size_t)g * N + n;
+      const int at = (n / NI) * (NI + PAD) + n % NI;
+      cp_async_16(&sB[buf][tt][at], row);
+      cp_async_16(&sC[buf][tt][at], row + (size_t)groups * N);
+    }
+    for (int idx = tid; idx < nt * pieces_x; idx += 64) {
+      const int tt = idx / pieces_x, j = idx % pieces_x;
+      if (p0 + j * V < P) cp_async_16(&sx[buf][tt][j * V], xbc + (size_t)(t0 + tt) * channels + (size_t)h * P + p0 + j * V);
+    }
+    cp_async_commit();
+  };
+  auto step_sizes = [&](int t0, int buf) {
+    if (tid < min(kScanChunk, end - t0)) {
+      const float zdt = to_float(u[(size_t)(t0 + tid) * ld_u + dt_col + h]) + bias;
+      const float dt = zdt > 20.f ? zdt : log1pf(expf(zdt));
+      sdt[buf][0][tid] = dt;
+      sdt[buf][1][tid] = expf(rate * dt);
+    }
+  };
+  issue(start, 0);
+  step_sizes(start, 0);
+  int buf = 0;
+  for (int t0 = start; t0 < end; t0 += kScanChunk, buf ^= 1) {
+    const int nt = min(kScanChunk, end - t0);
+    if (t0 + kScanChunk < end) {
+      issue(t0 + kScanChunk, buf ^ 1);
+      step_sizes(t0 + kScanChunk, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float dt = sdt[buf][0][tt], a = sdt[buf][1][tt];
+      const float xv = live ? to_float(sx[buf][tt][pl]) : 0.f;
+      const float dx = dt * xv;
+      const T* B = &sB[buf][tt][s * (NI + PAD)];
+      const T* C = &sC[buf][tt][s * (NI + PAD)];
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < NI; i += V) {
+        float bv[V], cv[V];
+        Vec<T>::load(B + i, bv);
+        Vec<T>::load(C + i, cv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          S[i + e] = fmaf(a, S[i + e], dx * bv[e]);
+          acc[e & 3] = fmaf(S[i + e], cv[e], acc[e & 3]);
+        }
+      }
+      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (live && s == 0) y[(size_t)(t0 + tt) * inner + (size_t)h * P + p] = fmaf(skip, xv, sum);
+    }
+    __syncthreads();      // the buffer may be filled again
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const int n = s * NI + i;
+      if (n < N) Sg[n] = S[i];
+    }
+  }
+}
+
 template <typename T>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ u, int64_t ld_u, const float* __restrict__ w,
                                         T* __restrict__ out, int inner, int groups, float eps) {
@@ -210,6 +335,27 @@ extern "C" int roost_mamba2_scan(const void* xbc, const void* u, int64_t ld_u, i
   if (heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "mamba2_scan: too many heads");
   if (rows == 0) return ROOST_OK;
   cudaStream_t s = (cudaStream_t)stream;
+  {
+    // whole 16-byte pieces everywhere: the form that reads shared memory in vectors and prefetches
+    const int vec = dtype == ROOST_F32 ? 4 : 8;
+    const int inner = heads * head_dim;
+    if (state_rows % vec == 0 && head_dim % vec == 0 && inner % vec == 0 && (groups * state_rows) % vec == 0 && (uintptr_t)xbc % 16 == 0 &&
+        (dtype == ROOST_F32 || dtype == ROOST_BF16) && (head_dim + kScanVecP - 1) / kScanVecP <= 65535) {
+      dim3 grid(rows, heads, (head_dim + kScanVecP - 1) / kScanVecP);
+      ROOST_DISPATCH_DTYPE(dtype, T, {
+        if (state_rows <= 64)
+          launch_kernel(mamba2_scan_vec_kernel<T, 16>, grid, dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, dt_col, y, dt_bias, a_log, d_skip,
+                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups);
+        else if (state_rows <= 128)
+          launch_kernel(mamba2_scan_vec_kernel<T, 32>, grid, dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, dt_col, y, dt_bias, a_log, d_skip,
+                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups);
+        else
+          launch_kernel(mamba2_scan_vec_kernel<T, 64>, grid, dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, dt_col, y, dt_bias, a_log, d_skip,
+                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups);
+      });
+      return check_launch("mamba2_scan");
+    }
+  }
   ROOST_DISPATCH_DTYPE(dtype, T, {
     if (state_rows <= 64)
       launch_scan<T, 16>(xbc, u, ld_u, dt_col, y, dt_bias, a_log, d_skip, state, state_stride, q_indptr, slots, rows, heads, head_dim, state_rows, groups, s);

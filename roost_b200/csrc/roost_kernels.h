@@ -289,9 +289,13 @@ int roost_gated_group_norm(const float* y, const void* u, int64_t ld_u, const fl
 
 /* ---- a feed-forward routed over experts (routed_experts.cu) ---- */
 int roost_moe_tile_rows(void);   /* rows of a tile of sorted rows */
-/* scratch: int32[2 * tokens * top]; tiles: int32[3 * max_tiles], max_tiles >= ceil(tokens * top / tile rows) + experts. */
+/* out[t, e] = x[t, :] . w[e, :] in 32-bit. */
+int roost_moe_router_logits(const void* x, const void* w, float* out, int tokens, int hidden, int experts, int dtype, roost_stream_t stream);
+/* scratch: int32[2 * tokens * top]; tiles: int32[3 * max_tiles], max_tiles >= ceil(tokens * top / tile rows) + experts;
+ * counts: int32[experts], zero on entry and left at zero. */
 int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
-                    int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, roost_stream_t stream);
+                    int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, int32_t* counts,
+                    roost_stream_t stream);
 int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
                            roost_stream_t stream);
 /* out[row, :] = a[row, :] w1[e]^T (w2 null) or silu(a w1[e]^T) * (a w2[e]^T), e the row's expert; w: [experts, n, k]. */

@@ -1,5 +1,6 @@
 // A feed-forward routed over experts, on the device from the router's logits to the summed outputs.
 //
+//   router_logits: z[t, e] = x[t, :] . W[e, :], a 32-bit sum whatever the activation dtype is.
 //   route:        per token the `top` largest logits choose its experts (ties to the lower index; the sigmoid is monotonic, so the
 //                 logits are compared); a pair (token, choice) gets the weight sigmoid(logit). Pairs are sorted by expert:
 //                 offsets[e] .. offsets[e+1] are expert e's rows; token_of / weight_of / expert_of give a sorted row's token,
@@ -10,64 +11,121 @@
 //                 rows on FFMA (every output sums over k in increasing order in one thread), and, for the few rows of a decode
 //                 step, a warp an output that streams the row's expert with 16-byte loads.
 //   combine:      out[t, :] = sum_k ys[inverse[t * top + k], :] (+ shared[t, :]), summed in 32-bit in the order of k.
-// One block does the routing: a step has at most a few thousand tokens and the work is a few comparisons each.
 #include "common.cuh"
+
+#include <mma.h>
 
 namespace roost {
 
 constexpr int kMoeTile = 64;
 constexpr int kMoeMaxTop = 32;
 
-__global__ void __launch_bounds__(1024) moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top,
-                                                        int32_t* __restrict__ token_of, float* __restrict__ weight_of,
-                                                        int32_t* __restrict__ expert_of, int32_t* __restrict__ inverse,
-                                                        int32_t* __restrict__ offsets, int32_t* __restrict__ tiles, int max_tiles,
-                                                        int32_t* __restrict__ pair_expert, int32_t* __restrict__ pair_rank) {
-  extern __shared__ int32_t counts[];      // [experts] counts, then [experts + 1] offsets
-  int32_t* offs = counts + experts;
+// Router logits: a warp a (token, expert), lanes stride over the hidden size with 16-byte loads, 32-bit sums.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_router_logits_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ out,
+                                                               int hidden, int experts) {
+  constexpr int V = Vec<T>::N;
   pdl_launch_dependents();
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.y * 8 + warp;
   pdl_wait();
-  __syncthreads();
-  for (int t = threadIdx.x; t < tokens; t += blockDim.x) {
-    const float* z = logits + (size_t)t * experts;
-    int chosen[kMoeMaxTop];
-    for (int k = 0; k < top; ++k) {
-      int best = -1;
-      float bz = 0.f;
-      for (int e = 0; e < experts; ++e) {
-        bool taken = false;
-        for (int c = 0; c < k; ++c) taken |= chosen[c] == e;
-        const float v = z[e];
-        if (!taken && (best < 0 || v > bz)) {
-          best = e;
-          bz = v;
-        }
+  if (e >= experts) return;
+  const T* xr = x + (size_t)t * hidden;
+  const T* wr = w + (size_t)e * hidden;
+  float s = 0.f;
+  if (hidden % V == 0 && ((uintptr_t)xr % 16 == 0) && ((uintptr_t)wr % 16 == 0)) {
+    for (int k = lane * V; k < hidden; k += 32 * V) {
+      float av[V], bv[V];
+      Vec<T>::load(xr + k, av);
+      Vec<T>::load(wr + k, bv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) s = fmaf(av[i], bv[i], s);
+    }
+  } else {
+    for (int k = lane; k < hidden; k += 32) s = fmaf(to_float(xr[k]), to_float(wr[k]), s);
+  }
+  s = warp_sum(s);
+  if (lane == 0) out[(size_t)t * experts + e] = s;
+}
+
+// A warp a token: the token's logits in shared memory, `top` rounds of a warp-wide argmax (ties to the lower index); the
+// choice's place among its expert's rows is the expert's running count (the order within an expert is that of arrival:
+// every row is computed for itself, so the order changes no value).
+__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int top,
+                                                      int32_t* __restrict__ pair_expert, int32_t* __restrict__ pair_rank,
+                                                      int32_t* __restrict__ counts) {
+  extern __shared__ float zs[];          // [8 warps][experts]
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + warp;
+  pdl_wait();
+  if (t >= tokens) return;
+  float* z = zs + (size_t)warp * experts;
+  for (int e = lane; e < experts; e += 32) {
+    const float v = logits[(size_t)t * experts + e];
+    z[e] = v == v ? fmaxf(v, -3.0e38f) : -3.0e38f;     // a NaN or -inf is the smallest score, not a hole in the order
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float bz = -INFINITY;
+    int best = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > bz) {
+        bz = v;
+        best = e;
       }
-      chosen[k] = best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float oz = __shfl_xor_sync(0xffffffffu, bz, o);
+      const int ob = __shfl_xor_sync(0xffffffffu, best, o);
+      if (oz > bz || (oz == bz && ob < best)) {
+        bz = oz;
+        best = ob;
+      }
+    }
+    if (lane == 0) {
+      z[best] = -INFINITY;               // taken
       pair_expert[(size_t)t * top + k] = best;
       pair_rank[(size_t)t * top + k] = atomicAdd(&counts[best], 1);
     }
+    __syncwarp();
   }
-  __syncthreads();
+}
+
+// One block: the experts' counts become their row ranges and the list of tiles, every pair goes to its sorted row, and the
+// counts are left at zero for the next call.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict__ logits, int tokens, int experts, int top,
+                                                       int32_t* __restrict__ token_of, float* __restrict__ weight_of,
+                                                       int32_t* __restrict__ expert_of, int32_t* __restrict__ inverse,
+                                                       int32_t* __restrict__ offsets, int32_t* __restrict__ tiles, int max_tiles,
+                                                       const int32_t* __restrict__ pair_expert, const int32_t* __restrict__ pair_rank,
+                                                       int32_t* __restrict__ counts) {
+  extern __shared__ int32_t offs[];      // [experts + 1]
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0) {
     int at = 0, n = 0;
     for (int e = 0; e < experts; ++e) {
+      const int c = counts[e];
       offs[e] = at;
       offsets[e] = at;
-      for (int r = at; r < at + counts[e]; r += kMoeTile) {
+      for (int r = at; r < at + c; r += kMoeTile) {
         tiles[3 * n] = e;
         tiles[3 * n + 1] = r;
-        tiles[3 * n + 2] = min(r + kMoeTile, at + counts[e]);
+        tiles[3 * n + 2] = min(r + kMoeTile, at + c);
         ++n;
       }
-      at += counts[e];
+      at += c;
     }
     offs[experts] = at;
     offsets[experts] = at;
     for (; n < max_tiles; ++n) tiles[3 * n] = -1;
   }
   __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
   for (int i = threadIdx.x; i < tokens * top; i += blockDim.x) {
     const int e = pair_expert[i];
     const int dest = offs[e] + pair_rank[i];
@@ -165,6 +223,108 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
   }
 }
 
+// The same tiles on the tensor cores for bfloat16 (mma.sync through the wmma fragments, 32-bit accumulators): four warps, a
+// 32 x 32 quarter of the tile each, k in steps of 32 staged in shared memory with the next step's loads in registers
+// meanwhile. Needs k a multiple of 8 (16-byte loads of whole rows). The accumulators leave through shared memory, where the
+// gated form applies silu(gate) * up to the two products rounded as outputs.
+template <bool GATED>
+__global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w1,
+                                                              const __nv_bfloat16* __restrict__ w2, __nv_bfloat16* __restrict__ out,
+                                                              const int32_t* __restrict__ tiles, int N, int K) {
+  using namespace nvcuda;
+  constexpr int BM = kMoeTile, BN = 64, BK = 32, LD = BK + 8, LDC = BN + 4;
+  constexpr int kStage = (BM + (GATED ? 2 : 1) * BN) * LD * 2;            // bytes of the operand tiles
+  constexpr int kOut = (GATED ? 2 : 1) * BM * LDC * 4;                    // bytes of the accumulators on their way out
+  __shared__ __align__(128) unsigned char raw[kStage > kOut ? kStage : kOut];
+  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(raw);
+  __nv_bfloat16* W1s = As + BM * LD;
+  __nv_bfloat16* W2s = W1s + BN * LD;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = tiles[3 * blockIdx.y];
+  if (e < 0) return;
+  const int m0 = tiles[3 * blockIdx.y + 1], m_end = tiles[3 * blockIdx.y + 2];
+  const int n0 = blockIdx.x * BN;
+  const __nv_bfloat16* wa = w1 + (size_t)e * N * K;
+  const __nv_bfloat16* wb = GATED ? w2 + (size_t)e * N * K : nullptr;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int wy = warp >> 1, wx = warp & 1;
+  // a thread moves two 16-byte pieces of each tile a step: rows tid / 4 and tid / 4 + 32, piece tid % 4
+  const int lr = tid >> 2, lc = (tid & 3) * 8;
+  uint4 ra[2], rb[2], rc[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = lr + 32 * i, k = k0 + lc;
+      const bool in_k = k < K;       // K is a multiple of 8: a piece is whole or absent
+      ra[i] = (in_k && m0 + row < m_end) ? *reinterpret_cast<const uint4*>(a + (size_t)(m0 + row) * K + k) : make_uint4(0, 0, 0, 0);
+      rb[i] = (in_k && n0 + row < N) ? *reinterpret_cast<const uint4*>(wa + (size_t)(n0 + row) * K + k) : make_uint4(0, 0, 0, 0);
+      if (GATED) rc[i] = (in_k && n0 + row < N) ? *reinterpret_cast<const uint4*>(wb + (size_t)(n0 + row) * K + k) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc1[2][2], acc2[GATED ? 2 : 1][2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      wmma::fill_fragment(acc1[i][j], 0.f);
+      if (GATED) wmma::fill_fragment(acc2[i][j], 0.f);
+    }
+  fetch(0);
+  for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int row = lr + 32 * i;
+      *reinterpret_cast<uint4*>(As + row * LD + lc) = ra[i];
+      *reinterpret_cast<uint4*>(W1s + row * LD + lc) = rb[i];
+      if (GATED) *reinterpret_cast<uint4*>(W2s + row * LD + lc) = rc[i];
+    }
+    __syncthreads();
+    if (k0 + BK < K) fetch(k0 + BK);
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa[2];
+      wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb[2], fc[GATED ? 2 : 1];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) wmma::load_matrix_sync(fa[i], As + (wy * 32 + i * 16) * LD + kk, LD);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        wmma::load_matrix_sync(fb[j], W1s + (wx * 32 + j * 16) * LD + kk, LD);
+        if (GATED) wmma::load_matrix_sync(fc[j], W2s + (wx * 32 + j * 16) * LD + kk, LD);
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          wmma::mma_sync(acc1[i][j], fa[i], fb[j], acc1[i][j]);
+          if (GATED) wmma::mma_sync(acc2[i][j], fa[i], fc[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+  float* C1 = reinterpret_cast<float*>(raw);
+  float* C2 = C1 + BM * LDC;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      wmma::store_matrix_sync(C1 + (wy * 32 + i * 16) * LDC + wx * 32 + j * 16, acc1[i][j], LDC, wmma::mem_row_major);
+      if (GATED) wmma::store_matrix_sync(C2 + (wy * 32 + i * 16) * LDC + wx * 32 + j * 16, acc2[i][j], LDC, wmma::mem_row_major);
+    }
+  __syncthreads();
+  for (int idx = tid; idx < BM * BN; idx += 128) {
+    const int r = idx / BN, c = idx % BN;
+    const int m = m0 + r, n = n0 + c;
+    if (m >= m_end || n >= N) continue;
+    float v = C1[r * LDC + c];
+    if (GATED) {
+      const float g = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(C2[r * LDC + c]));
+      v = g / (1.0f + expf(-g)) * up;
+    }
+    out[(size_t)m * N + n] = __float2bfloat16_rn(v);
+  }
+}
+
 // Few rows: a block per sorted row and 8 outputs, a warp an output; lanes stride over k.
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
@@ -233,15 +393,32 @@ using namespace roost;
 
 extern "C" int roost_moe_tile_rows(void) { return kMoeTile; }
 
+extern "C" int roost_moe_router_logits(const void* x, const void* w, float* out, int tokens, int hidden, int experts, int dtype,
+                                       roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && hidden > 0 && experts > 0, "moe_router_logits: sizes must be positive");
+  if (tokens == 0) return ROOST_OK;
+  dim3 grid(tokens, (experts + 7) / 8);
+  if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_router_logits: too many experts");
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(moe_router_logits_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)x, (const T*)w, out,
+                                               hidden, experts));
+  return check_launch("moe_router_logits");
+}
+
+// counts: int32[experts], zero on entry and left at zero (a caller keeps one buffer for all its calls on a stream).
 extern "C" int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
-                               int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, roost_stream_t stream) {
+                               int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, int32_t* counts,
+                               roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts, "moe_route: sizes do not fit");
   if (top > kMoeMaxTop || experts > 4096) return fail(ROOST_ERR_UNSUPPORTED, "moe_route: more than 32 choices a token or 4096 experts");
   ROOST_REQUIRE((int64_t)max_tiles >= ((int64_t)tokens * top + kMoeTile - 1) / kMoeTile + experts, "moe_route: the tile list is too short");
+  ROOST_REQUIRE(counts != nullptr && scratch != nullptr, "moe_route: a pointer is null");
   if (tokens == 0) return ROOST_OK;
-  const size_t smem = ((size_t)2 * experts + 1) * sizeof(int32_t);
-  launch_kernel(moe_route_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, logits, tokens, experts, top, token_of, weight_of, expert_of,
-                inverse, offsets, tiles, max_tiles, scratch, scratch + (size_t)tokens * top);
+  int32_t* pair_expert = scratch;
+  int32_t* pair_rank = scratch + (size_t)tokens * top;
+  launch_kernel(moe_topk_kernel, dim3((tokens + 7) / 8), dim3(256), (size_t)8 * experts * sizeof(float), (cudaStream_t)stream, logits, tokens,
+                experts, top, pair_expert, pair_rank, counts);
+  launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), ((size_t)experts + 1) * sizeof(int32_t), (cudaStream_t)stream, logits, tokens, experts, top,
+                token_of, weight_of, expert_of, inverse, offsets, tiles, max_tiles, (const int32_t*)pair_expert, (const int32_t*)pair_rank, counts);
   return check_launch("moe_route");
 }
 
@@ -263,6 +440,12 @@ extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* 
   if (form == 0) {
     dim3 grid((n + 63) / 64, max_tiles);
     if (max_tiles > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_expert_gemm: more than 65535 tiles of rows");
+    if (dtype == ROOST_BF16 && k % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w1 % 16 == 0 && (uintptr_t)w2 % 16 == 0) {
+      using B = __nv_bfloat16;
+      if (w2) launch_kernel(moe_tile_gemm_tc_kernel<true>, grid, dim3(128), 0, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+      else launch_kernel(moe_tile_gemm_tc_kernel<false>, grid, dim3(128), 0, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+      return check_launch("moe_expert_gemm");
+    }
     ROOST_DISPATCH_DTYPE(dtype, T, {
       if (w2) launch_kernel(moe_tile_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k);
       else launch_kernel(moe_tile_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k);

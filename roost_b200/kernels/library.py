@@ -119,7 +119,9 @@ _SIGNATURES = {
                           c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_gated_group_norm": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_moe_tile_rows": [],
-    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "roost_moe_router_logits": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                        c_void_p],
     "roost_moe_gather_scale": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -608,9 +610,24 @@ class KernelLibrary:
         return out
 
     # ------------------------------------------------------------------ routed experts
+    def moe_router_logits(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """x W^T as 32-bit sums, float32 [tokens, experts]."""
+        _need(x, "x"); _need(w, "w", x.dtype)
+        T, H = x.shape
+        E = w.shape[0]
+        if w.shape[1] != H:
+            raise KernelError("moe_router_logits: x and the router's weight differ in width")
+        out = torch.empty((T, E), dtype=torch.float32, device=x.device)
+        self._call("roost_moe_router_logits", _ptr(x), _ptr(w), _ptr(out), T, H, E, dtype_code(x.dtype), _stream())
+        return out
+
     def moe_route(self, logits: torch.Tensor, top: int) -> MoeRoute:
         _need(logits, "logits", torch.float32)
         T, E = logits.shape
+        counts = getattr(self, "_moe_counts", None)
+        if counts is None or counts.device != logits.device:
+            # the experts' running counts: zero between calls (the sorting kernel leaves them so), allocated once, outside any capture
+            counts = self._moe_counts = torch.zeros(4096, dtype=torch.int32, device=logits.device)
         rows = T * top
         tile = self._lib.roost_moe_tile_rows()
         max_tiles = -(-rows // tile) + E
@@ -623,7 +640,7 @@ class KernelLibrary:
         scratch = ints[at : at + 2 * rows]
         weight = torch.empty((rows,), dtype=torch.float32, device=dev)
         self._call("roost_moe_route", _ptr(logits), T, E, top, _ptr(token), _ptr(weight), _ptr(expert), _ptr(inverse), _ptr(offsets), _ptr(tiles),
-                   max_tiles, _ptr(scratch), _stream())
+                   max_tiles, _ptr(scratch), _ptr(counts), _stream(), launches=2)
         return MoeRoute(top=top, rows=rows, token=token, weight=weight, expert=expert, inverse=inverse, offsets=offsets, tiles=tiles,
                         max_tiles=max_tiles, form=0)
 

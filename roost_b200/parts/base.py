@@ -29,6 +29,9 @@ class ParamDecl:
     # "matrix": converted to the compute dtype; "vector": kept in its stored dtype (32-bit stays 32-bit) in the
     # bfloat16 path; "table": integer tables become int32. In the 32-bit path every float becomes float32.
     role: str = "matrix"
+    # how the random-weights mode draws the parameter when the role's default (matrices N(0, std), vectors 1 + N(0, norm_std))
+    # does not suit it: ("normal", mean, std) or ("uniform", low, high)
+    init: tuple | None = None
 
 
 @dataclass(frozen=True)

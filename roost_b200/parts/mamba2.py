@@ -54,10 +54,12 @@ class Mamba2(Mixer):
         s = spec
         inner = s.num_heads * s.head_dim
         channels = inner + 2 * s.groups * s.state
-        v = lambda *shape: ParamDecl(shape=shape, role="vector")
-        return {"in": ParamDecl(shape=(2 * inner + 2 * s.groups * s.state + s.num_heads, s.hidden)), "conv": v(channels, s.conv_taps),
-                "conv_bias": v(channels), "dt_bias": v(s.num_heads), "A_log": v(s.num_heads), "D": v(s.num_heads), "norm": v(inner),
-                "out": ParamDecl(shape=(s.hidden, inner))}
+        v = lambda *shape, init=None: ParamDecl(shape=shape, role="vector", init=init)
+        # the random-weights mode draws rates and steps with which a state lives for hundreds of tokens
+        return {"in": ParamDecl(shape=(2 * inner + 2 * s.groups * s.state + s.num_heads, s.hidden)),
+                "conv": v(channels, s.conv_taps, init=("normal", 0.0, 0.4)), "conv_bias": v(channels, init=("normal", 0.0, 0.1)),
+                "dt_bias": v(s.num_heads, init=("normal", -1.0, 0.5)), "A_log": v(s.num_heads, init=("uniform", -3.0, -0.5)),
+                "D": v(s.num_heads), "norm": v(inner), "out": ParamDecl(shape=(s.hidden, inner))}
 
     def load(self, params):
         f = lambda name: params[name].float().contiguous()

@@ -47,7 +47,7 @@ class LayerNorm(Norm):
 
     @classmethod
     def parameters(cls, spec: NormSpec):
-        return {"weight": ParamDecl(shape=(spec.size,), role="vector"), "bias": ParamDecl(shape=(spec.size,), role="vector")}
+        return {"weight": ParamDecl(shape=(spec.size,), role="vector"), "bias": ParamDecl(shape=(spec.size,), role="vector", init=("normal", 0.0, 0.05))}
 
     def load(self, params):
         self.weight = params["weight"].float().contiguous()

@@ -65,7 +65,7 @@ class RoutedMlp(FeedForward):
 
     def __call__(self, x, batch=None):
         s, k = self.spec, self.rt.kernels
-        logits = k.gemm_simt(x, self.router, torch.float32)                     # 32-bit sums, whatever the activation dtype
+        logits = k.moe_router_logits(x, self.router)                            # 32-bit sums, whatever the activation dtype
         route = k.moe_route(logits, s.top)
         xs = k.moe_gather_scale(x, route)                                       # [T * top, hidden]: score * row, sorted by expert
         act = k.moe_expert_gate_up(xs, self.gate, self.up, route)               # [T * top, ff]

@@ -41,16 +41,19 @@ def random_tensors(config: dict, seed: int, std: float = 0.02, norm_std: float =
     spec = arch.to_spec(cfg, None)
     decls = parameter_declarations(spec)
     shapes = expected_tensors(decls, spec.weight_names)
-    roles = {}
+    roles, inits = {}, {}
     for scope, params in decls.items():
         for local, decl in params.items():
             for n in spec.weight_names[scope][local]:
                 roles[n] = decl.role
+                inits[n] = decl.init
     dtype = _DTYPES[spec.stored_dtype]
     out = {}
     for name, shape in shapes.items():
         g = torch.Generator().manual_seed(_tensor_seed(seed, name))
-        if roles[name] == "vector":
+        if inits[name] is not None:
+            t = _draw(inits[name], shape, g, "cpu")
+        elif roles[name] == "vector":
             t = torch.ones(shape, dtype=torch.float32)
             if norm_std > 0:
                 t += torch.randn(shape, generator=g, dtype=torch.float32) * norm_std
@@ -58,6 +61,16 @@ def random_tensors(config: dict, seed: int, std: float = 0.02, norm_std: float =
             t = torch.randn(shape, generator=g, dtype=torch.float32) * std
         out[name] = t.to(dtype)
     return out
+
+
+def _draw(init: tuple, shape, generator, device) -> torch.Tensor:
+    """A parameter drawn as its declaration asks: ("normal", mean, std) or ("uniform", low, high), in float32."""
+    kind, a, b = init
+    if kind == "normal":
+        return a + b * torch.randn(shape, generator=generator, dtype=torch.float32, device=device)
+    if kind == "uniform":
+        return a + (b - a) * torch.rand(shape, generator=generator, dtype=torch.float32, device=device)
+    raise ValueError(f"a parameter asks to be drawn as '{kind}'; known: normal, uniform")
 
 
 REFERENCE_TINY_SEED = 0x524F4F53540001   # the seed of the reference's dense tiny model (src/Starlings.Roost.Models.Tiny/TinyConfig.cs:63-66)
@@ -132,7 +145,9 @@ def random_parameters(spec, seed: int, device, dtype: torch.dtype, std: float = 
         out[scope] = {}
         for local, decl in params.items():
             g = torch.Generator(device=device).manual_seed(_tensor_seed(seed, f"{scope}.{local}"))
-            if decl.role == "vector":
+            if decl.init is not None:
+                out[scope][local] = _draw(decl.init, decl.shape, g, device).to(dtype)
+            elif decl.role == "vector":
                 t = torch.ones(decl.shape, dtype=torch.float32, device=device)
                 if norm_std > 0:
                     t += torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * norm_std

@@ -213,6 +213,9 @@ class FakeKernels:
         return (g.reshape(T, inner) * w).to(out_dtype)
 
     # ---- routed experts
+    def moe_router_logits(self, x, w):
+        return x.float() @ w.float().t()
+
     def moe_route(self, logits, top):
         from types import SimpleNamespace
         T, E = logits.shape
