@@ -274,6 +274,15 @@ int roost_latent_attention(const void* q_latent, const void* q, void* out, float
                            int nope, int rope, int rank, int page_size, float scale, int window, int splits, int dtype,
                            roost_stream_t stream);
 
+/* The same on the tensor cores for bfloat16 steps of many tokens (latent_attention_tc.cu): q_indptr[b] .. q_indptr[b+1] are
+ * the tokens of batch row b (batch_rows rows). Serves nope and rope that are multiples of 8 and a rank that is a multiple of
+ * 16 up to 512. */
+int roost_latent_attention_tc_supported(int nope, int rope, int rank);
+int roost_latent_attention_tc(const void* q_latent, const void* q, void* out, const void* pool, const int32_t* positions,
+                              const int32_t* q_indptr, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens,
+                              int batch_rows, int heads, int nope, int rope, int rank, int page_size, float scale, int window,
+                              roost_stream_t stream);
+
 /* ---- the Mamba-2 recurrence (mamba2.cu; the layout of a state slot and the formulas are at the top of that file) ---- */
 int roost_mamba2_conv(const void* u, int64_t ld, int col, void* out, const float* w, const float* bias, const float* state,
                       int64_t state_stride, int conv_off, const int32_t* token_row, const int32_t* q_indptr, const int32_t* slots,

@@ -112,6 +112,9 @@ _SIGNATURES = {
                              c_float, c_int, c_void_p],
     "roost_latent_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+    "roost_latent_attention_tc_supported": [c_int, c_int, c_int],
+    "roost_latent_attention_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_mamba2_conv": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int,
                           c_int, c_int, c_int, c_void_p],
     "roost_mamba2_conv_state": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -560,8 +563,13 @@ class KernelLibrary:
         tiles = -(-max(reach, 1) // 32) + 1
         return max(1, min(self._decode_ctas // max(blocks, 1), tiles, 32))
 
+    LATENT_TC_MIN_ROWS = 128    # packed (token, head) rows from which a bfloat16 step runs the tensor-core form
+
     def latent_attention(self, q_latent, q, pool, positions, token_row, kv_indptr, kv_indices, heads, nope, rope, rank, scale, window,
-                         kv_cap: int = 0, few_rows: bool = False) -> torch.Tensor:
+                         kv_cap: int = 0, few_rows: bool = False, q_indptr: torch.Tensor | None = None) -> torch.Tensor:
+        """Attention in the latent space: out [heads, tokens, rank]. bfloat16 steps of many tokens (prompt portions) run on
+        the tensor cores where the sizes allow; steps of few rows (decode) and float32 run the 32-bit form, a token's keys
+        dealt to several blocks when the step alone would not fill the device."""
         _need(q_latent, "q_latent"); _need(q, "q", q_latent.dtype); _need(pool, "pool", q.dtype)
         for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
             _need(t, n, torch.int32)
@@ -569,6 +577,13 @@ class KernelLibrary:
         if tuple(q_latent.shape) != (heads, T, rank) or pool.shape[-1] != rank + rope or pool.shape[1] != 1:
             raise KernelError("latent_attention: q_latent or the pool do not fit the sizes")
         out = torch.empty((heads, T, rank), dtype=q.dtype, device=q.device)
+        if (q.dtype == torch.bfloat16 and q_indptr is not None and not few_rows and T * heads >= self.LATENT_TC_MIN_ROWS
+                and self._lib.roost_latent_attention_tc_supported(nope, rope, rank)):
+            _need(q_indptr, "q_indptr", torch.int32)
+            self._call("roost_latent_attention_tc", _ptr(q_latent), _ptr(q), _ptr(out), _ptr(pool), _ptr(positions), _ptr(q_indptr),
+                       _ptr(kv_indptr), _ptr(kv_indices), T, q_indptr.numel() - 1, heads, nope, rope, rank, pool.shape[2], scale,
+                       int(window) if window else 0, _stream())
+            return out
         splits = self.latent_splits_for(T, heads, window, kv_cap) if kv_cap else 1
         part = torch.empty((T * heads * splits * (rank + 2),), dtype=torch.float32, device=q.device) if splits > 1 else None
         self._call("roost_latent_attention", _ptr(q_latent), _ptr(q), _ptr(out), _ptr(part), _ptr(pool), _ptr(positions), _ptr(token_row),

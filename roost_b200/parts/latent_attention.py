@@ -90,7 +90,7 @@ class LatentAttention(Mixer):
         q_latent = torch.empty((H, T, s.kv_rank), dtype=q.dtype, device=q.device)
         batched_linear(self.rt, q_heads[:, :, : s.nope_dim], self.key_up, q_latent)
         o_latent = k.latent_attention(q_latent, q, cache.k_pool, batch.positions, batch.token_row, tables.kv_indptr, tables.kv_indices,
-                                      H, s.nope_dim, s.rope_dim, s.kv_rank, s.scale, s.window, batch.kv_cap, batch.all_single)
+                                      H, s.nope_dim, s.rope_dim, s.kv_rank, s.scale, s.window, batch.kv_cap, batch.all_single, batch.q_indptr)
         o = torch.empty((T, H * s.v_dim), dtype=q.dtype, device=q.device)
         batched_linear(self.rt, o_latent, self.value_up, o.view(T, H, s.v_dim).transpose(0, 1))
         return self.out(o)

@@ -142,7 +142,7 @@ class FakeKernels:
                 if slot >= 0:
                     pool[slot // page_size, 0, slot % page_size] = entry[t]
 
-    def latent_attention(self, q_latent, q, pool, positions, token_row, kv_indptr, kv_indices, heads, nope, rope, rank, scale, window, kv_cap=0, few_rows=False):
+    def latent_attention(self, q_latent, q, pool, positions, token_row, kv_indptr, kv_indices, heads, nope, rope, rank, scale, window, kv_cap=0, few_rows=False, q_indptr=None):
         T = q.shape[0]
         page = pool.shape[2]
         out = torch.zeros(heads, T, rank, dtype=q.dtype)

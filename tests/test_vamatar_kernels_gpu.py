@@ -99,6 +99,61 @@ def test_latent_attention_with_split_keys_against_the_plain_sum(kernels, dtype, 
     close(split, want, dtype, "latent attention, split keys", bf16=1e-2)
 
 
+@pytest.mark.parametrize("rank", [32, 80, 272])
+@pytest.mark.parametrize("window", [None, 37])
+def test_latent_attention_on_the_tensor_cores_against_the_plain_sum(kernels, rank, window):
+    """Portions of three requests in one step (77 tokens after 60 cached ones, 5 from the start, 140 after 3), five heads, so
+    that the packed (token, head) rows of a tile span several tokens with windows of their own; pages of 8 in a scrambled
+    order; with a window the pages it has passed are gone from the block tables (-1)."""
+    heads, nope, rope, page = 5, 8, 8, 8
+    g = torch.Generator().manual_seed(rank)
+    spans = [(60, 77), (0, 5), (3, 140)]
+    totals = [a + n for a, n in spans]
+    n_pages = sum(-(-n // page) for n in totals)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    pool = torch.zeros(n_pages, 1, page, rank + rope)
+    tables, entries = [], []
+    for (start, n), total in zip(spans, totals):
+        e = torch.randn(total, rank + rope, generator=g)
+        mine = [order.pop() for _ in range(-(-total // page))]
+        for j in range(total):
+            pool[mine[j // page], 0, j % page] = e[j]
+        if window:            # pages wholly before the first query's window are given back
+            for i in range(max(0, start - window + 1) // page):
+                pool[mine[i]] = float("nan")
+                mine[i] = -1
+        entries.append(e)
+        tables.append(mine)
+    pool = pool.to(torch.bfloat16).cuda()
+    T = sum(n for _, n in spans)
+    q_latent = torch.randn(heads, T, rank, generator=g).to(torch.bfloat16).cuda()
+    q = torch.randn(T, heads * (nope + rope), generator=g).to(torch.bfloat16).cuda()
+    positions = torch.tensor([start + i for start, n in spans for i in range(n)], dtype=torch.int32).cuda()
+    token_row = torch.tensor([b for b, (_, n) in enumerate(spans) for _ in range(n)], dtype=torch.int32).cuda()
+    q_indptr = torch.tensor([0] + list(np.cumsum([n for _, n in spans])), dtype=torch.int32).cuda()
+    indptr = torch.tensor([0] + list(np.cumsum([len(t) for t in tables])), dtype=torch.int32).cuda()
+    indices = torch.tensor([p for t in tables for p in t], dtype=torch.int32).cuda()
+    scale = 0.3
+    want = torch.zeros(heads, T, rank, dtype=torch.float64)
+    t = 0
+    for b, (start, n) in enumerate(spans):
+        e = entries[b].to(torch.bfloat16).double()
+        for i in range(n):
+            pos = start + i
+            lo = 0 if window is None else max(0, pos - window + 1)
+            rows = e[lo : pos + 1]
+            qr = q[t].double().cpu().reshape(heads, nope + rope)[:, nope:]
+            sc = (q_latent[:, t].double().cpu() @ rows[:, :rank].T + qr @ rows[:, rank:].T) * scale
+            want[:, t] = torch.softmax(sc, -1) @ rows[:, :rank]
+            t += 1
+    got = kernels.latent_attention(q_latent, q, pool, positions, token_row, indptr, indices, heads, nope, rope, rank, scale, window, 1024,
+                                   False, q_indptr)
+    assert kernels._lib.roost_latent_attention_tc_supported(nope, rope, rank) and T * heads >= kernels.LATENT_TC_MIN_ROWS
+    close(got, want, torch.bfloat16, f"latent attention on the tensor cores, rank {rank}", bf16=1.5e-2)
+    slow = kernels.latent_attention(q_latent, q, pool, positions, token_row, indptr, indices, heads, nope, rope, rank, scale, window, 0)
+    close(slow, want, torch.bfloat16, "the 32-bit form on the same step", bf16=1e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_routing_chooses_the_largest_scores_and_sorts_the_pairs_by_expert(kernels, dtype):
     T, E, top, hidden, ff = 50, 9, 3, 24, 16
