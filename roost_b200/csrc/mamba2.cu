@@ -152,12 +152,22 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-template <typename T, int NI>
+//
+// Long rows are cut into chunks of kScanChunkTokens tokens that run side by side (a single row of a prompt would keep two
+// warps an SM busy otherwise): MODE 1 walks every chunk from a zero state and leaves the chunk's own state and the product
+// of its decays; a carry kernel then gives every chunk the state it starts from, S_in(c+1) = (product of c's decays) S_in(c)
+// + S_own(c), and the slot its new state; MODE 2 walks the chunks again from those states and writes y. MODE 0 is the
+// walk of whole rows in one pass (decode steps and short portions). A block of MODE 1 or 2 finds its (row, chunk) by
+// walking q_indptr; blocks beyond the step's chunks leave at once.
+constexpr int kScanChunkTokens = 128;
+
+template <typename T, int NI, int MODE>
 __global__ void __launch_bounds__(64) mamba2_scan_vec_kernel(const T* __restrict__ xbc, const T* __restrict__ u, int64_t ld_u, int dt_col,
                                                             float* __restrict__ y, const float* __restrict__ dt_bias,
                                                             const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state,
                                                             int64_t state_stride, const int32_t* __restrict__ q_indptr,
-                                                            const int32_t* __restrict__ slots, int heads, int P, int N, int groups) {
+                                                            const int32_t* __restrict__ slots, int heads, int P, int N, int groups,
+                                                            float* __restrict__ ws_state, float* __restrict__ ws_decay, int batch_rows) {
   constexpr int V = Vec<T>::N;                    // elements of a 16-byte piece
   constexpr int PAD = V;                          // a quarter's run is followed by one piece: the quarters fall in different banks
   constexpr int ROW = kScanSlices * (NI + PAD);   // elements of a token's B (or C) in shared memory
@@ -165,15 +175,41 @@ __global__ void __launch_bounds__(64) mamba2_scan_vec_kernel(const T* __restrict
   __shared__ __align__(16) T sC[2][kScanChunk][ROW];
   __shared__ __align__(16) T sx[2][kScanChunk][kScanVecP];
   __shared__ float sdt[2][2][kScanChunk];
+  __shared__ int item[2];
   pdl_launch_dependents();
-  const int r = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * kScanVecP;
+  const int h = blockIdx.y, p0 = blockIdx.z * kScanVecP;
   const int g = h / (heads / groups);
   const int inner = heads * P, channels = inner + 2 * groups * N;
   const int tid = threadIdx.x;
   const int pl = tid / kScanSlices, s = tid % kScanSlices;     // the thread's value within the block, and its quarter
   const int p = p0 + pl;
   const bool live = p < P;
-  const int start = q_indptr[r], end = q_indptr[r + 1];
+  int r = blockIdx.x, start, end;
+  if (MODE == 0) {
+    start = q_indptr[r];
+    end = q_indptr[r + 1];
+  } else {
+    if (tid == 0) {
+      int at = 0, found = -1, c = 0;
+      for (int b = 0; b < batch_rows; ++b) {
+        const int n = (q_indptr[b + 1] - q_indptr[b] + kScanChunkTokens - 1) / kScanChunkTokens;
+        if ((int)blockIdx.x < at + n) {
+          found = b;
+          c = (int)blockIdx.x - at;
+          break;
+        }
+        at += n;
+      }
+      item[0] = found;
+      item[1] = c;
+    }
+    __syncthreads();
+    r = item[0];
+    if (r < 0) return;
+    start = q_indptr[r] + item[1] * kScanChunkTokens;
+    end = min(start + kScanChunkTokens, q_indptr[r + 1]);
+  }
+  float* Win = MODE == 0 ? nullptr : ws_state + (((size_t)blockIdx.x * heads + h) * P + (live ? p : 0)) * N;
   const float bias = dt_bias[h], rate = -expf(a_log[h]), skip = d_skip[h];
   float* Sg = state + (size_t)slots[r] * state_stride + ((size_t)h * P + (live ? p : 0)) * N;
   // pieces beyond the state's rows stay zero for the whole walk
@@ -187,8 +223,9 @@ __global__ void __launch_bounds__(64) mamba2_scan_vec_kernel(const T* __restrict
 #pragma unroll
   for (int i = 0; i < NI; ++i) {
     const int n = s * NI + i;
-    S[i] = (live && n < N) ? Sg[n] : 0.f;
+    S[i] = (MODE != 1 && live && n < N) ? (MODE == 0 ? Sg[n] : Win[n]) : 0.f;
   }
+  float decays = 1.0f;
   __syncthreads();
   const int pieces_n = N / V;                      // pieces of a token's B
   const int pieces_x = kScanVecP / V;
@@ -233,6 +270,7 @@ __global__ void __launch_bounds__(64) mamba2_scan_vec_kernel(const T* __restrict
       const float dt = sdt[buf][0][tt], a = sdt[buf][1][tt];
       const float xv = live ? to_float(sx[buf][tt][pl]) : 0.f;
       const float dx = dt * xv;
+      if (MODE == 1) decays *= a;
       const T* B = &sB[buf][tt][s * (NI + PAD)];
       const T* C = &sC[buf][tt][s * (NI + PAD)];
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -247,20 +285,51 @@ __global__ void __launch_bounds__(64) mamba2_scan_vec_kernel(const T* __restrict
           acc[e & 3] = fmaf(S[i + e], cv[e], acc[e & 3]);
         }
       }
-      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (live && s == 0) y[(size_t)(t0 + tt) * inner + (size_t)h * P + p] = fmaf(skip, xv, sum);
+      if (MODE != 1) {
+        float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (live && s == 0) y[(size_t)(t0 + tt) * inner + (size_t)h * P + p] = fmaf(skip, xv, sum);
+      }
     }
     __syncthreads();      // the buffer may be filled again
   }
+  if (MODE == 2) return;
+  float* dst = MODE == 0 ? Sg : Win;
   if (live) {
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
       const int n = s * NI + i;
-      if (n < N) Sg[n] = S[i];
+      if (n < N) dst[n] = S[i];
     }
   }
+  if (MODE == 1 && tid == 0 && blockIdx.z == 0) ws_decay[(size_t)blockIdx.x * heads + h] = decays;
+}
+
+// Between the two walks of the chunks: per row and element of the state, in chunk order, the state a chunk starts from
+// replaces the chunk's own in the workspace; the row's slot gets the state after its last chunk.
+__global__ void mamba2_chunk_carry_kernel(float* __restrict__ ws_state, const float* __restrict__ ws_decay, float* state, int64_t state_stride,
+                                          const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ slots, int heads, int P, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x;
+  const size_t per = (size_t)heads * P * N;
+  const size_t e = (size_t)blockIdx.y * blockDim.x + threadIdx.x;
+  if (e >= per) return;
+  int first = 0;
+  for (int i = 0; i < b; ++i) first += (q_indptr[i + 1] - q_indptr[i] + kScanChunkTokens - 1) / kScanChunkTokens;
+  const int chunks = (q_indptr[b + 1] - q_indptr[b] + kScanChunkTokens - 1) / kScanChunkTokens;
+  if (chunks == 0) return;
+  const int h = (int)(e / ((size_t)P * N));
+  float* slot = state + (size_t)slots[b] * state_stride + e;
+  float run = *slot;
+  for (int c = 0; c < chunks; ++c) {
+    float* w = ws_state + (size_t)(first + c) * per + e;
+    const float own = *w;
+    *w = run;
+    run = fmaf(ws_decay[(size_t)(first + c) * heads + h], run, own);
+  }
+  *slot = run;
 }
 
 template <typename T>
@@ -328,7 +397,8 @@ static void launch_scan(const void* xbc, const void* u, int64_t ld_u, int dt_col
 
 extern "C" int roost_mamba2_scan(const void* xbc, const void* u, int64_t ld_u, int dt_col, float* y, const float* dt_bias, const float* a_log,
                                  const float* d_skip, float* state, int64_t state_stride, const int32_t* q_indptr, const int32_t* slots,
-                                 int rows, int heads, int head_dim, int state_rows, int groups, int dtype, roost_stream_t stream) {
+                                 int rows, int tokens, int heads, int head_dim, int state_rows, int groups, float* ws_state, float* ws_decay,
+                                 int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && heads > 0 && head_dim > 0 && state_rows > 0 && groups > 0 && heads % groups == 0, "mamba2_scan: sizes do not fit");
   if (state_rows > 256) return fail(ROOST_ERR_UNSUPPORTED, "mamba2_scan: a state of more than 256 rows");
   if (head_dim > 128) return fail(ROOST_ERR_UNSUPPORTED, "mamba2_scan: heads of more than 128 values");
@@ -340,19 +410,31 @@ extern "C" int roost_mamba2_scan(const void* xbc, const void* u, int64_t ld_u, i
     const int vec = dtype == ROOST_F32 ? 4 : 8;
     const int inner = heads * head_dim;
     if (state_rows % vec == 0 && head_dim % vec == 0 && inner % vec == 0 && (groups * state_rows) % vec == 0 && (uintptr_t)xbc % 16 == 0 &&
-        (dtype == ROOST_F32 || dtype == ROOST_BF16) && (head_dim + kScanVecP - 1) / kScanVecP <= 65535) {
-      dim3 grid(rows, heads, (head_dim + kScanVecP - 1) / kScanVecP);
+        (dtype == ROOST_F32 || dtype == ROOST_BF16) && (head_dim + kScanVecP - 1) / kScanVecP <= 65535 && rows <= 65535) {
+      const int zdim = (head_dim + kScanVecP - 1) / kScanVecP;
+      const long long chunks = (long long)(tokens + kScanChunkTokens - 1) / kScanChunkTokens + rows;     // an upper bound
+      const bool chunked = ws_state != nullptr && tokens >= 4 * kScanChunkTokens && chunks <= 65535 * 32;
+#define ROOST_SCAN_VEC(NI, MODE, GRIDX)                                                                                                     \
+  launch_kernel(mamba2_scan_vec_kernel<T, NI, MODE>, dim3((unsigned)(GRIDX), heads, zdim), dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, \
+                dt_col, y, dt_bias, a_log, d_skip, state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups, ws_state, ws_decay, rows)
       ROOST_DISPATCH_DTYPE(dtype, T, {
-        if (state_rows <= 64)
-          launch_kernel(mamba2_scan_vec_kernel<T, 16>, grid, dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, dt_col, y, dt_bias, a_log, d_skip,
-                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups);
-        else if (state_rows <= 128)
-          launch_kernel(mamba2_scan_vec_kernel<T, 32>, grid, dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, dt_col, y, dt_bias, a_log, d_skip,
-                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups);
-        else
-          launch_kernel(mamba2_scan_vec_kernel<T, 64>, grid, dim3(64), 0, s, (const T*)xbc, (const T*)u, ld_u, dt_col, y, dt_bias, a_log, d_skip,
-                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows, groups);
+        if (!chunked) {
+          if (state_rows <= 64) ROOST_SCAN_VEC(16, 0, rows);
+          else if (state_rows <= 128) ROOST_SCAN_VEC(32, 0, rows);
+          else ROOST_SCAN_VEC(64, 0, rows);
+        } else {
+          if (state_rows <= 64) ROOST_SCAN_VEC(16, 1, chunks);
+          else if (state_rows <= 128) ROOST_SCAN_VEC(32, 1, chunks);
+          else ROOST_SCAN_VEC(64, 1, chunks);
+          const size_t per = (size_t)heads * head_dim * state_rows;
+          launch_kernel(mamba2_chunk_carry_kernel, dim3(rows, (unsigned)((per + 255) / 256)), dim3(256), 0, s, ws_state, (const float*)ws_decay,
+                        state, state_stride, q_indptr, slots, heads, head_dim, state_rows);
+          if (state_rows <= 64) ROOST_SCAN_VEC(16, 2, chunks);
+          else if (state_rows <= 128) ROOST_SCAN_VEC(32, 2, chunks);
+          else ROOST_SCAN_VEC(64, 2, chunks);
+        }
       });
+#undef ROOST_SCAN_VEC
       return check_launch("mamba2_scan");
     }
   }
@@ -366,6 +448,8 @@ extern "C" int roost_mamba2_scan(const void* xbc, const void* u, int64_t ld_u, i
   });
   return check_launch("mamba2_scan");
 }
+
+extern "C" int roost_mamba2_scan_chunks(int tokens, int rows) { return (tokens + kScanChunkTokens - 1) / kScanChunkTokens + rows; }
 
 extern "C" int roost_gated_group_norm(const float* y, const void* u, int64_t ld_u, const float* w, void* out, int tokens, int inner, int groups,
                                       float eps, int dtype, roost_stream_t stream) {

@@ -292,7 +292,12 @@ int roost_mamba2_conv_state(const void* u, int64_t ld, int col, float* state, in
                             roost_stream_t stream);
 int roost_mamba2_scan(const void* xbc, const void* u, int64_t ld_u, int dt_col, float* y, const float* dt_bias, const float* a_log,
                       const float* d_skip, float* state, int64_t state_stride, const int32_t* q_indptr, const int32_t* slots,
-                      int rows, int heads, int head_dim, int state_rows, int groups, int dtype, roost_stream_t stream);
+                      int rows, int tokens, int heads, int head_dim, int state_rows, int groups, float* ws_state, float* ws_decay,
+                      int dtype, roost_stream_t stream);
+/* With ws_state (float[chunks * heads * head_dim * state_rows]) and ws_decay (float[chunks * heads]), chunks =
+ * roost_mamba2_scan_chunks(tokens, rows), roost_mamba2_scan cuts long rows into chunks that run side by side; with null
+ * pointers it walks every row in one pass. */
+int roost_mamba2_scan_chunks(int tokens, int rows);
 int roost_gated_group_norm(const float* y, const void* u, int64_t ld_u, const float* w, void* out, int tokens, int inner, int groups,
                            float eps, int dtype, roost_stream_t stream);
 

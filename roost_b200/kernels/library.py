@@ -119,7 +119,8 @@ _SIGNATURES = {
                           c_int, c_int, c_int, c_void_p],
     "roost_mamba2_conv_state": [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_mamba2_scan": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
-                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "roost_mamba2_scan_chunks": [c_int, c_int],
     "roost_gated_group_norm": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_moe_tile_rows": [],
     "roost_moe_router_logits": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -605,15 +606,22 @@ class KernelLibrary:
         self._call("roost_mamba2_conv_state", _ptr(u), u.stride(0), col, _ptr(state), state.stride(0), conv_off, _ptr(q_indptr), _ptr(slots),
                    slots.numel(), channels, taps, dtype_code(u.dtype), _stream(), launches=1 if taps > 1 else 0)
 
+    SCAN_CHUNKED_MIN_TOKENS = 512
+
     def mamba2_scan(self, xbc, u, dt_col, dt_bias, a_log, d, state, q_indptr, slots, heads, head_dim, state_rows, groups) -> torch.Tensor:
         _need(xbc, "xbc"); _need(u, "u", xbc.dtype); _need(state, "state", torch.float32)
         for n, t in (("dt_bias", dt_bias), ("A_log", a_log), ("D", d)):
             _need(t, n, torch.float32)
         T = xbc.shape[0]
         y = torch.empty((T, heads * head_dim), dtype=torch.float32, device=xbc.device)
+        ws_state = ws_decay = None
+        if T >= self.SCAN_CHUNKED_MIN_TOKENS:       # long rows are cut into chunks that run side by side
+            chunks = self._lib.roost_mamba2_scan_chunks(T, slots.numel())
+            ws_state = torch.empty((chunks * heads * head_dim * state_rows,), dtype=torch.float32, device=xbc.device)
+            ws_decay = torch.empty((chunks * heads,), dtype=torch.float32, device=xbc.device)
         self._call("roost_mamba2_scan", _ptr(xbc), _ptr(u), u.stride(0), dt_col, _ptr(y), _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(state),
-                   state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), heads, head_dim, state_rows, groups, dtype_code(xbc.dtype),
-                   _stream())
+                   state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), T, heads, head_dim, state_rows, groups, _ptr(ws_state),
+                   _ptr(ws_decay), dtype_code(xbc.dtype), _stream(), launches=3 if ws_state is not None else 1)
         return y
 
     def gated_group_norm(self, y, u, w, groups, eps, out_dtype) -> torch.Tensor:

@@ -214,6 +214,31 @@ def test_the_recurrence_at_sizes_of_every_register_class(tmp_path, state, vdim):
     assert H.scaled_error(got, want) < 2e-4 and H.rms_error(got, want) < 3e-5
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_rows_cut_into_chunks_that_run_side_by_side(tmp_path, kernels, dtype):
+    """A step of 700 + 41 + 130 tokens (three requests, the second and third continuing earlier portions) is long enough for
+    the recurrence to cut its rows into chunks: the states the chunks start from, the carried state of each request and the
+    decoding that follows must be those of a walk token by token."""
+    cfg = VM.config([(VM.mamba(heads=4, vdim=32, state=64, groups=2, conv=4, norm_groups=2), None),
+                     (VM.mamba(heads=2, vdim=16, state=16, groups=1, conv=3, norm_groups=1), VM.dense(ff=32))], width=64, vocab=90, cap=None)
+    tensors = VM.draw_tensors(cfg, 31)
+    folder = VM.write_model(tmp_path, cfg, tensors)
+    model = H.make_model(folder, dtype, "gpu")
+    ex = StepExecutor(model, page_size=16, num_pages=8, max_requests=3)
+    a, b, c = H.random_ids(703, cfg["vocab"], 1), H.random_ids(60, cfg["vocab"], 2), H.random_ids(140, cfg["vocab"], 3)
+    assert sum(map(len, (a[:700], b[16:57], c[7:137]))) >= kernels.SCAN_CHUNKED_MIN_TOKENS
+    ex.step([StepEntry("b", b[:16], []), StepEntry("c", c[:7], [])])
+    out = ex.step([StepEntry("a", a[:700], [0, 127, 128, 699]), StepEntry("b", b[16:57], [40]), StepEntry("c", c[7:137], [0, 129])])
+    tail = [ex.step([StepEntry("a", [a[700 + i]], [0]), StepEntry("b", [b[57 + i]], [0]), StepEntry("c", [c[137 + i]], [0])]) for i in range(3)]
+    w = VM.plain_weights(tensors)
+    wa, wb, wc = P.forward(cfg, w, a), P.forward(cfg, w, b), P.forward(cfg, w, c)
+    want = torch.cat([wa[[0, 127, 128, 699]], wb[[56]], wc[[7, 136]]] + [torch.stack([wa[700 + i], wb[57 + i], wc[137 + i]]) for i in range(3)])
+    got = torch.cat([out] + tail)
+    err, rms = H.scaled_error(got, want), H.rms_error(got, want)
+    print(f"MEASURED chunked recurrence {dtype}: worst {err:.3e}, rms {rms:.3e}")
+    assert (err < 1e-4 and rms < 1e-5) if dtype == torch.float32 else (err < 0.25 and rms < 0.04)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_replay_tool_on_a_vamatar_folder(tmp_path, dtype):
     cfg = VM.WIDE
