@@ -323,11 +323,21 @@ __global__ void mamba2_chunk_carry_kernel(float* __restrict__ ws_state, const fl
   const int h = (int)(e / ((size_t)P * N));
   float* slot = state + (size_t)slots[b] * state_stride + e;
   float run = *slot;
-  for (int c = 0; c < chunks; ++c) {
-    float* w = ws_state + (size_t)(first + c) * per + e;
-    const float own = *w;
-    *w = run;
-    run = fmaf(ws_decay[(size_t)(first + c) * heads + h], run, own);
+  for (int c0 = 0; c0 < chunks; c0 += 8) {        // eight chunks' values are loaded before the first is needed
+    float own[8], decay[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool in = c0 + j < chunks;
+      own[j] = in ? ws_state[(size_t)(first + c0 + j) * per + e] : 0.f;
+      decay[j] = in ? ws_decay[(size_t)(first + c0 + j) * heads + h] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (c0 + j < chunks) {
+        ws_state[(size_t)(first + c0 + j) * per + e] = run;
+        run = fmaf(decay[j], run, own[j]);
+      }
+    }
   }
   *slot = run;
 }

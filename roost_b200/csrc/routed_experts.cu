@@ -223,22 +223,27 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
   }
 }
 
-// The same tiles on the tensor cores for bfloat16 (mma.sync through the wmma fragments, 32-bit accumulators): four warps, a
-// 32 x 32 quarter of the tile each, k in steps of 32 staged in shared memory with the next step's loads in registers
-// meanwhile. Needs k a multiple of 8 (16-byte loads of whole rows). The accumulators leave through shared memory, where the
-// gated form applies silu(gate) * up to the two products rounded as outputs.
+// The same rows on the tensor cores for bfloat16 (mma.sync through the wmma fragments, 32-bit accumulators): a block takes a
+// tile of 64 sorted rows and 128 outputs, four warps with 64 x 32 each (a fragment of the rows serves two or four products);
+// k in steps of 32 through three stages of shared memory filled by cp.async. Needs k a multiple of 8 (16-byte pieces of whole
+// rows). A warp's accumulators leave through a patch of shared memory of its own, where the gated form applies
+// silu(gate) * up to the two products rounded as outputs.
+__device__ __forceinline__ void moe_cp16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+
+constexpr int kMoeTcBN = 128, kMoeTcBK = 32, kMoeTcLD = kMoeTcBK + 8, kMoeTcStages = 3;
+constexpr int moe_tc_stage_elems(bool gated) { return (kMoeTile + (gated ? 2 : 1) * kMoeTcBN) * kMoeTcLD; }
+
 template <bool GATED>
 __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w1,
                                                               const __nv_bfloat16* __restrict__ w2, __nv_bfloat16* __restrict__ out,
                                                               const int32_t* __restrict__ tiles, int N, int K) {
   using namespace nvcuda;
-  constexpr int BM = kMoeTile, BN = 64, BK = 32, LD = BK + 8, LDC = BN + 4;
-  constexpr int kStage = (BM + (GATED ? 2 : 1) * BN) * LD * 2;            // bytes of the operand tiles
-  constexpr int kOut = (GATED ? 2 : 1) * BM * LDC * 4;                    // bytes of the accumulators on their way out
-  __shared__ __align__(128) unsigned char raw[kStage > kOut ? kStage : kOut];
-  __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(raw);
-  __nv_bfloat16* W1s = As + BM * LD;
-  __nv_bfloat16* W2s = W1s + BN * LD;
+  constexpr int BM = kMoeTile, BN = kMoeTcBN, BK = kMoeTcBK, LD = kMoeTcLD, STAGE = moe_tc_stage_elems(GATED);
+  extern __shared__ __align__(128) unsigned char raw[];
+  __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(raw);
   pdl_launch_dependents();
   pdl_wait();
   const int e = tiles[3 * blockIdx.y];
@@ -247,82 +252,100 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
   const int n0 = blockIdx.x * BN;
   const __nv_bfloat16* wa = w1 + (size_t)e * N * K;
   const __nv_bfloat16* wb = GATED ? w2 + (size_t)e * N * K : nullptr;
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int wy = warp >> 1, wx = warp & 1;
-  // a thread moves two 16-byte pieces of each tile a step: rows tid / 4 and tid / 4 + 32, piece tid % 4
-  const int lr = tid >> 2, lc = (tid & 3) * 8;
-  uint4 ra[2], rb[2], rc[2];
-  auto fetch = [&](int k0) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int row = lr + 32 * i, k = k0 + lc;
-      const bool in_k = k < K;       // K is a multiple of 8: a piece is whole or absent
-      ra[i] = (in_k && m0 + row < m_end) ? *reinterpret_cast<const uint4*>(a + (size_t)(m0 + row) * K + k) : make_uint4(0, 0, 0, 0);
-      rb[i] = (in_k && n0 + row < N) ? *reinterpret_cast<const uint4*>(wa + (size_t)(n0 + row) * K + k) : make_uint4(0, 0, 0, 0);
-      if (GATED) rc[i] = (in_k && n0 + row < N) ? *reinterpret_cast<const uint4*>(wb + (size_t)(n0 + row) * K + k) : make_uint4(0, 0, 0, 0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  auto fill = [&](int k0, int st) {
+    __nv_bfloat16* As = stages + (size_t)st * STAGE;
+    __nv_bfloat16* W1s = As + BM * LD;
+    __nv_bfloat16* W2s = W1s + BN * LD;
+    if (k0 < K) {
+      for (int idx = tid; idx < (BM + (GATED ? 2 : 1) * BN) * 4; idx += 128) {       // 16-byte pieces: four a row
+        const int row = idx >> 2, k = k0 + (idx & 3) * 8;
+        __nv_bfloat16* dst = As + row * LD + (idx & 3) * 8;        // the three tiles lie back to back with one row stride
+        const __nv_bfloat16* src = nullptr;
+        if (k < K) {
+          if (row < BM) src = m0 + row < m_end ? a + (size_t)(m0 + row) * K + k : nullptr;
+          else if (row < BM + BN) src = n0 + row - BM < N ? wa + (size_t)(n0 + row - BM) * K + k : nullptr;
+          else src = n0 + row - BM - BN < N ? wb + (size_t)(n0 + row - BM - BN) * K + k : nullptr;
+        }
+        if (src) moe_cp16(dst, src);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      }
     }
+    asm volatile("cp.async.commit_group;\n" ::);
   };
-  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc1[2][2], acc2[GATED ? 2 : 1][2];
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc1[4][2], acc2[GATED ? 4 : 1][2];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       wmma::fill_fragment(acc1[i][j], 0.f);
       if (GATED) wmma::fill_fragment(acc2[i][j], 0.f);
     }
-  fetch(0);
+  fill(0, 0);
+  fill(BK, 1);
+  int st = 0;
   for (int k0 = 0; k0 < K; k0 += BK) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int row = lr + 32 * i;
-      *reinterpret_cast<uint4*>(As + row * LD + lc) = ra[i];
-      *reinterpret_cast<uint4*>(W1s + row * LD + lc) = rb[i];
-      if (GATED) *reinterpret_cast<uint4*>(W2s + row * LD + lc) = rc[i];
-    }
+    fill(k0 + 2 * BK, (st + 2) % kMoeTcStages);        // an empty group beyond k keeps the count of groups in step
+    asm volatile("cp.async.wait_group 2;\n" ::);
     __syncthreads();
-    if (k0 + BK < K) fetch(k0 + BK);
+    const __nv_bfloat16* As = stages + (size_t)st * STAGE;
+    const __nv_bfloat16* W1s = As + BM * LD;
+    const __nv_bfloat16* W2s = W1s + BN * LD;
 #pragma unroll
     for (int kk = 0; kk < BK; kk += 16) {
-      wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa[2];
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa[4];
       wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb[2], fc[GATED ? 2 : 1];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) wmma::load_matrix_sync(fa[i], As + (wy * 32 + i * 16) * LD + kk, LD);
+      for (int i = 0; i < 4; ++i) wmma::load_matrix_sync(fa[i], As + (i * 16) * LD + kk, LD);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        wmma::load_matrix_sync(fb[j], W1s + (wx * 32 + j * 16) * LD + kk, LD);
-        if (GATED) wmma::load_matrix_sync(fc[j], W2s + (wx * 32 + j * 16) * LD + kk, LD);
+        wmma::load_matrix_sync(fb[j], W1s + (warp * 32 + j * 16) * LD + kk, LD);
+        if (GATED) wmma::load_matrix_sync(fc[j], W2s + (warp * 32 + j * 16) * LD + kk, LD);
       }
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           wmma::mma_sync(acc1[i][j], fa[i], fb[j], acc1[i][j]);
           if (GATED) wmma::mma_sync(acc2[i][j], fa[i], fc[j], acc2[i][j]);
         }
     }
-    __syncthreads();
+    __syncthreads();      // the stage may be filled again
+    st = (st + 1) % kMoeTcStages;
   }
-  float* C1 = reinterpret_cast<float*>(raw);
-  float* C2 = C1 + BM * LDC;
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  __syncthreads();
+  // a warp's patch: two 16 x 16 blocks of floats with rows of 20
+  float* patch = reinterpret_cast<float*>(raw) + warp * 2 * 16 * 20;
+  const int pr = lane >> 1, pc = (lane & 1) * 8;        // a lane's row of the block and its eight columns
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
-      wmma::store_matrix_sync(C1 + (wy * 32 + i * 16) * LDC + wx * 32 + j * 16, acc1[i][j], LDC, wmma::mem_row_major);
-      if (GATED) wmma::store_matrix_sync(C2 + (wy * 32 + i * 16) * LDC + wx * 32 + j * 16, acc2[i][j], LDC, wmma::mem_row_major);
+      wmma::store_matrix_sync(patch, acc1[i][j], 20, wmma::mem_row_major);
+      if (GATED) wmma::store_matrix_sync(patch + 16 * 20, acc2[i][j], 20, wmma::mem_row_major);
+      __syncwarp();
+      const int m = m0 + i * 16 + pr, n = n0 + warp * 32 + j * 16 + pc;
+      if (m < m_end) {
+        float v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          v[c] = patch[pr * 20 + pc + c];
+          if (GATED) {
+            const float g = __bfloat162float(__float2bfloat16_rn(v[c]));
+            const float up = __bfloat162float(__float2bfloat16_rn(patch[16 * 20 + pr * 20 + pc + c]));
+            v[c] = g / (1.0f + expf(-g)) * up;
+          }
+        }
+        __nv_bfloat16* dst = out + (size_t)m * N + n;
+        if (n + 8 <= N && N % 8 == 0) {
+          Vec<__nv_bfloat16>::store(dst, v);
+        } else {
+          for (int c = 0; c < 8 && n + c < N; ++c) dst[c] = __float2bfloat16_rn(v[c]);
+        }
+      }
+      __syncwarp();
     }
-  __syncthreads();
-  for (int idx = tid; idx < BM * BN; idx += 128) {
-    const int r = idx / BN, c = idx % BN;
-    const int m = m0 + r, n = n0 + c;
-    if (m >= m_end || n >= N) continue;
-    float v = C1[r * LDC + c];
-    if (GATED) {
-      const float g = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(C2[r * LDC + c]));
-      v = g / (1.0f + expf(-g)) * up;
-    }
-    out[(size_t)m * N + n] = __float2bfloat16_rn(v);
-  }
 }
 
 // Few rows: a block per sorted row and 8 outputs, a warp an output; lanes stride over k.
@@ -440,10 +463,18 @@ extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* 
   if (form == 0) {
     dim3 grid((n + 63) / 64, max_tiles);
     if (max_tiles > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_expert_gemm: more than 65535 tiles of rows");
-    if (dtype == ROOST_BF16 && k % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w1 % 16 == 0 && (uintptr_t)w2 % 16 == 0) {
+    if (dtype == ROOST_BF16 && k % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w1 % 16 == 0 && (uintptr_t)w2 % 16 == 0 &&
+        (uintptr_t)out % 16 == 0) {
       using B = __nv_bfloat16;
-      if (w2) launch_kernel(moe_tile_gemm_tc_kernel<true>, grid, dim3(128), 0, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
-      else launch_kernel(moe_tile_gemm_tc_kernel<false>, grid, dim3(128), 0, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+      dim3 tc_grid((n + kMoeTcBN - 1) / kMoeTcBN, max_tiles);
+      const size_t smem = (size_t)kMoeTcStages * moe_tc_stage_elems(w2 != nullptr) * sizeof(B);
+      if (w2) {
+        cudaFuncSetAttribute(moe_tile_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_kernel(moe_tile_gemm_tc_kernel<true>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+      } else {
+        cudaFuncSetAttribute(moe_tile_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        launch_kernel(moe_tile_gemm_tc_kernel<false>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+      }
       return check_launch("moe_expert_gemm");
     }
     ROOST_DISPATCH_DTYPE(dtype, T, {

@@ -262,3 +262,26 @@ def test_the_replay_tool_on_a_vamatar_folder(tmp_path, dtype):
     assert H.scaled_error(read(0, 2), wa[[0, 32]]) < bound
     assert H.scaled_error(read(2, 2), torch.stack([wa[68], wb[40]])) < bound
     assert H.scaled_error(read(3, 1), wa[69:70]) < bound
+
+
+def test_the_command_line_writes_a_vamatar_folder_and_generates_from_it(tmp_path):
+    """random-weights draws the folder from the configuration alone (decay rates and step biases by their declarations' hints),
+    generate runs it through the entry point; the greedy tokens are the plain implementation's wherever its choice is clear."""
+    roost = lambda *a: subprocess.run([sys.executable, str(ROOT / "bin" / "roost"), *a], capture_output=True, text=True, timeout=600)
+    (tmp_path / "config.json").write_text(json.dumps(VM.MIXED))
+    r = roost("random-weights", "--config", str(tmp_path / "config.json"), "--out", str(tmp_path / "model"), "--seed", "4", "--std", "0.2",
+              "--norm-std", "0.1")
+    assert r.returncode == 0, r.stderr
+    cfg, w = P.load_model_dir(tmp_path / "model")
+    assert -3.0 <= float(w["l1.mix.A_log"].min()) and float(w["l1.mix.A_log"].max()) <= -0.5
+    prompt = H.random_ids(21, cfg["vocab"], 6)
+    r = roost("generate", "--model", str(tmp_path / "model"), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+              "--max-output-tokens", "8", "--ignore-eos", "--attention-blocks", "16", "--max-sequences", "2")
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["finish_reason"] == "length" and len(out["token_ids"]) == 8
+    logits = P.forward(cfg, w, prompt + out["token_ids"][:-1])
+    for j, tok in enumerate(out["token_ids"]):
+        top = logits[len(prompt) - 1 + j].topk(2)
+        if float(top.values[0] - top.values[1]) > 1e-3:
+            assert tok == int(top.indices[0]), (j, tok, int(top.indices[0]))
