@@ -234,6 +234,172 @@ __global__ void __launch_bounds__(192, 1)
   }
 }
 
+// The grouped form: the rows of a are sorted by the expert they belong to and cut into tiles of at most 128 rows that meet one
+// expert each (tile_list: (expert, first row, one past the last row) triples, expert -1 for the unused tail of the list);
+// w holds the experts' matrices one after the other ([experts * N, K], so expert e's rows start at e * N). A tile of a is
+// loaded from its first row whatever that is (rows beyond the expert's are computed and not stored); a tile of w that runs
+// past the expert's N rows reads the next expert's and those columns are not stored either. Everything else is the kernel
+// above: the same roles, stages, accumulators, epilogues and bounded waits.
+template <typename TOut, int EPI>
+__global__ void __launch_bounds__(192, 1)
+    gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, TOut* __restrict__ out,
+                                const int32_t* __restrict__ tile_list, int m_tiles, int N, int K, int64_t ldo) {
+  extern __shared__ unsigned char smem_raw[];
+  // tiles want 1024-byte alignment (the swizzle pattern repeats every 1024 bytes)
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_base_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  const int n_tiles = (N + BN - 1) / BN;
+  const int k_blocks = (K + BK - 1) / BK;
+  const int tiles = m_tiles * n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int mt = t % m_tiles;
+        const int e = tile_list[3 * mt];
+        if (e < 0) continue;
+        const int m0 = tile_list[3 * mt + 1], n0 = (t / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(sa, &tma_a, full_bar(stage), kb * BK, m0);
+          tma_load_2d(sa + kStageABytes, &tma_b, full_bar(stage), kb * BK, e * N + n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        if (tile_list[3 * (t % m_tiles)] < 0) continue;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        ++it;
+        if (!(ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abortp, 2))) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = umma_desc_k_major_sw128(sa);
+          const uint64_t b_desc = umma_desc_k_major_sw128(sa + kStageABytes);
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            // inside the 128-byte swizzle row a step of 16 elements is 32 bytes: two 16-byte units of the address field
+            tcgen05_mma_f16(tmem_d, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar(stage));  // the stage is free once these products have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tcgen05_commit(acc_full_bar(acc));
+      }
+    }
+  } else {
+    // epilogue warps 2..5; warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
+    const int lane_group = warp & 3;
+    const bool vec_ok = (ldo * (int64_t)sizeof(TOut)) % 16 == 0 && ((uintptr_t)out % 16) == 0;
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      const int mt = t % m_tiles;
+      if (tile_list[3 * mt] < 0) continue;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      ++it;
+      const int m0 = tile_list[3 * mt + 1], M = tile_list[3 * mt + 2], n0 = (t / m_tiles) * BN;
+      if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
+      tcgen05_fence_after();
+      const int row = m0 + lane_group * 32 + lane;
+      if (EPI == 0) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+          const int col = n0 + c * 32;
+          if (row < M && col < N) store_row32<TOut>(out + (size_t)row * ldo + col, v, N - col, vec_ok);
+        }
+      } else {
+        const int n_out = N / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), g);
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + BN / 2 + c * 32), u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]));
+          const int col = n0 / 2 + c * 32;
+          if (row < M && col < n_out) store_row32<TOut>(out + (size_t)row * ldo + col, g, n_out - col, vec_ok);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+  }
+
+  // common exit: on an abort give copies in flight time to land before shared memory is released
+  __syncwarp();
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(256);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ CTA pairs
 // The same product with two CTAs (a cluster of two SMs) on one 256 x 256 tile: tcgen05.mma.cta_group::2 multiplies the
 // pair's 256 rows of a by 256 rows of w, of which each CTA stages its own 128 rows of a and 128 rows of w, so a CTA
@@ -1116,6 +1282,46 @@ extern "C" int roost_gemm_tcgen05_status(void) {
     cudaMemcpyToSymbol(g_gemm_tcgen05_error, &zero, sizeof(int));
   }
   return code;
+}
+
+template <int EPI>
+static int launch_tcgen05_grouped(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const int32_t* tile_list, int m_tiles, int n, int k,
+                                  int64_t ldo, cudaStream_t s) {
+  static int sms = 0;
+  static bool attr_set = false;
+  const size_t smem = (size_t)STAGES * kStageBytes + 1024;
+  auto kernel = gemm_tcgen05_grouped_kernel<__nv_bfloat16, EPI>;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  const long long tiles = (long long)m_tiles * ((n + BN - 1) / BN);
+  const int grid = tiles < sms ? (int)tiles : sms;
+  kernel<<<grid, 192, smem, s>>>(ma, mb, (__nv_bfloat16*)out, tile_list, m_tiles, n, k, ldo);
+  return check_launch("gemm_tcgen05_grouped");
+}
+
+// Rows of a sorted by expert against the experts' matrices w [experts, n, k] (contiguous): out[row, :] = a[row, :] w[e]^T, or
+// with swiglu (n = 2 * inter, an expert's rows interleaved in blocks of 128 gate rows then their 128 up rows)
+// out[row, :] = silu(gate) * up of n / 2 columns. tile_list: m_tiles triples (expert, first row, one past the last row) of at
+// most 128 rows each, expert -1 for unused entries.
+extern "C" int roost_gemm_tcgen05_grouped(const void* a, const void* w, void* out, const int32_t* tile_list, int m_tiles, int rows,
+                                          int experts, int n, int k, int swiglu, roost_stream_t stream) {
+  ROOST_REQUIRE(rows > 0 && experts > 0 && n > 0 && k > 0 && m_tiles > 0 && tile_list != nullptr, "gemm_tcgen05_grouped: sizes must be positive");
+  if (k % 8 != 0 || (swiglu && n % 256 != 0) || (long long)experts * n > 2147483647LL) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_tcgen05_grouped: k must be a multiple of 8 and, with swiglu, n a multiple of 256");
+  }
+  ROOST_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0), "gemm_tcgen05_grouped: pointers must be 16-byte aligned");
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, rows, k, k, BM);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mb, w, experts * n, k, k, BN);
+  if (rc != ROOST_OK) return rc;
+  if (swiglu) return launch_tcgen05_grouped<1>(ma, mb, out, tile_list, m_tiles, n, k, n / 2, (cudaStream_t)stream);
+  return launch_tcgen05_grouped<0>(ma, mb, out, tile_list, m_tiles, n, k, n, (cudaStream_t)stream);
 }
 
 extern "C" int roost_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw, int64_t ldo,

@@ -307,9 +307,17 @@ int roost_moe_tile_rows(void);   /* rows of a tile of sorted rows */
 int roost_moe_router_logits(const void* x, const void* w, float* out, int tokens, int hidden, int experts, int dtype, roost_stream_t stream);
 /* scratch: int32[2 * tokens * top]; tiles: int32[3 * max_tiles], max_tiles >= ceil(tokens * top / tile rows) + experts;
  * counts: int32[experts], zero on entry and left at zero. */
+/* wide_tiles (may be null): the same rows cut into tiles of roost_moe_wide_tile_rows() rows, int32[3 * max_wide_tiles], for
+ * roost_gemm_tcgen05_grouped. */
+int roost_moe_wide_tile_rows(void);
 int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
-                    int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, int32_t* counts,
-                    roost_stream_t stream);
+                    int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* wide_tiles, int max_wide_tiles,
+                    int32_t* scratch, int32_t* counts, roost_stream_t stream);
+/* Sorted rows against the experts' matrices w [experts, n, k] on tcgen05 (gemm_tcgen05.cu): out[row, :] = a[row, :] w[e]^T, or
+ * with swiglu (n = 2 * inter, an expert's rows in blocks of 128 gate rows then their 128 up rows) silu(gate) * up of n / 2
+ * columns. tile_list: the route's wide tiles. k a multiple of 8; with swiglu n a multiple of 256. */
+int roost_gemm_tcgen05_grouped(const void* a, const void* w, void* out, const int32_t* tile_list, int m_tiles, int rows, int experts,
+                               int n, int k, int swiglu, roost_stream_t stream);
 int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
                            roost_stream_t stream);
 /* out[row, :] = a[row, :] w1[e]^T (w2 null) or silu(a w1[e]^T) * (a w2[e]^T), e the row's expert; w: [experts, n, k]. */

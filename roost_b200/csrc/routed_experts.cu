@@ -18,6 +18,7 @@
 namespace roost {
 
 constexpr int kMoeTile = 64;
+constexpr int kMoeWideTile = 128;
 constexpr int kMoeMaxTop = 32;
 
 // Router logits: a warp a (token, expert), lanes stride over the hidden size with 16-byte loads, 32-bit sums.
@@ -101,6 +102,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
                                                        int32_t* __restrict__ token_of, float* __restrict__ weight_of,
                                                        int32_t* __restrict__ expert_of, int32_t* __restrict__ inverse,
                                                        int32_t* __restrict__ offsets, int32_t* __restrict__ tiles, int max_tiles,
+                                                       int32_t* __restrict__ wide_tiles, int max_wide_tiles,
                                                        const int32_t* __restrict__ pair_expert, const int32_t* __restrict__ pair_rank,
                                                        int32_t* __restrict__ counts) {
   extern __shared__ int32_t offs[];      // [experts + 1]
@@ -123,6 +125,20 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
     offs[experts] = at;
     offsets[experts] = at;
     for (; n < max_tiles; ++n) tiles[3 * n] = -1;
+  }
+  if (threadIdx.x == 32 && wide_tiles != nullptr) {      // the same rows in tiles of kMoeWideTile, for the tcgen05 product
+    int at = 0, n = 0;
+    for (int e = 0; e < experts; ++e) {
+      const int c = counts[e];
+      for (int r = at; r < at + c; r += kMoeWideTile) {
+        wide_tiles[3 * n] = e;
+        wide_tiles[3 * n + 1] = r;
+        wide_tiles[3 * n + 2] = min(r + kMoeWideTile, at + c);
+        ++n;
+      }
+      at += c;
+    }
+    for (; n < max_wide_tiles; ++n) wide_tiles[3 * n] = -1;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
@@ -428,20 +444,25 @@ extern "C" int roost_moe_router_logits(const void* x, const void* w, float* out,
 }
 
 // counts: int32[experts], zero on entry and left at zero (a caller keeps one buffer for all its calls on a stream).
+extern "C" int roost_moe_wide_tile_rows(void) { return kMoeWideTile; }
+
 extern "C" int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
-                               int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* scratch, int32_t* counts,
-                               roost_stream_t stream) {
+                               int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* wide_tiles, int max_wide_tiles,
+                               int32_t* scratch, int32_t* counts, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts, "moe_route: sizes do not fit");
   if (top > kMoeMaxTop || experts > 4096) return fail(ROOST_ERR_UNSUPPORTED, "moe_route: more than 32 choices a token or 4096 experts");
   ROOST_REQUIRE((int64_t)max_tiles >= ((int64_t)tokens * top + kMoeTile - 1) / kMoeTile + experts, "moe_route: the tile list is too short");
   ROOST_REQUIRE(counts != nullptr && scratch != nullptr, "moe_route: a pointer is null");
+  ROOST_REQUIRE(wide_tiles == nullptr || (int64_t)max_wide_tiles >= ((int64_t)tokens * top + kMoeWideTile - 1) / kMoeWideTile + experts,
+                "moe_route: the list of wide tiles is too short");
   if (tokens == 0) return ROOST_OK;
   int32_t* pair_expert = scratch;
   int32_t* pair_rank = scratch + (size_t)tokens * top;
   launch_kernel(moe_topk_kernel, dim3((tokens + 7) / 8), dim3(256), (size_t)8 * experts * sizeof(float), (cudaStream_t)stream, logits, tokens,
                 experts, top, pair_expert, pair_rank, counts);
   launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), ((size_t)experts + 1) * sizeof(int32_t), (cudaStream_t)stream, logits, tokens, experts, top,
-                token_of, weight_of, expert_of, inverse, offsets, tiles, max_tiles, (const int32_t*)pair_expert, (const int32_t*)pair_rank, counts);
+                token_of, weight_of, expert_of, inverse, offsets, tiles, max_tiles, wide_tiles, max_wide_tiles, (const int32_t*)pair_expert,
+                (const int32_t*)pair_rank, counts);
   return check_launch("moe_route");
 }
 

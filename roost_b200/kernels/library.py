@@ -124,8 +124,10 @@ _SIGNATURES = {
     "roost_gated_group_norm": [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_moe_tile_rows": [],
     "roost_moe_router_logits": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                        c_void_p],
+    "roost_moe_wide_tile_rows": [],
+    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                        c_void_p, c_void_p, c_void_p],
+    "roost_gemm_tcgen05_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_gather_scale": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
@@ -152,8 +154,11 @@ class MoeRoute:
     tiles: torch.Tensor
     max_tiles: int
     form: int
+    wide_tiles: torch.Tensor | None = None     # the same rows in tiles of 128, for the tcgen05 product of steps of many rows
+    max_wide_tiles: int = 0
 
 
+MOE_TCGEN05_MIN_ROWS = 1024  # sorted rows from which a bfloat16 step runs the experts' products on tcgen05
 MOE_ROW_FORM_MAX_ROWS = 64   # sorted rows up to which a bfloat16 step streams each row's expert instead of tiling the rows
 
 
@@ -655,17 +660,20 @@ class KernelLibrary:
         tile = self._lib.roost_moe_tile_rows()
         max_tiles = -(-rows // tile) + E
         dev = logits.device
-        ints = torch.empty((4 * rows + (E + 1) + 3 * max_tiles + 2 * rows,), dtype=torch.int32, device=dev)
+        wide = self._lib.roost_moe_wide_tile_rows()
+        max_wide = (-(-rows // wide) + E) if rows >= MOE_TCGEN05_MIN_ROWS else 0
+        ints = torch.empty((4 * rows + (E + 1) + 3 * max_tiles + 3 * max_wide + 2 * rows,), dtype=torch.int32, device=dev)
         token, expert, inverse = ints[:rows], ints[rows : 2 * rows], ints[2 * rows : 3 * rows]
         at = 3 * rows
         offsets, at = ints[at : at + E + 1], at + E + 1
         tiles, at = ints[at : at + 3 * max_tiles], at + 3 * max_tiles
+        wide_tiles, at = (ints[at : at + 3 * max_wide] if max_wide else None), at + 3 * max_wide
         scratch = ints[at : at + 2 * rows]
         weight = torch.empty((rows,), dtype=torch.float32, device=dev)
         self._call("roost_moe_route", _ptr(logits), T, E, top, _ptr(token), _ptr(weight), _ptr(expert), _ptr(inverse), _ptr(offsets), _ptr(tiles),
-                   max_tiles, _ptr(scratch), _ptr(counts), _stream(), launches=2)
+                   max_tiles, _ptr(wide_tiles), max_wide, _ptr(scratch), _ptr(counts), _stream(), launches=2)
         return MoeRoute(top=top, rows=rows, token=token, weight=weight, expert=expert, inverse=inverse, offsets=offsets, tiles=tiles,
-                        max_tiles=max_tiles, form=0)
+                        max_tiles=max_tiles, form=0, wide_tiles=wide_tiles, max_wide_tiles=max_wide)
 
     def moe_gather_scale(self, x: torch.Tensor, route: MoeRoute) -> torch.Tensor:
         _need(x, "x")
@@ -685,11 +693,26 @@ class KernelLibrary:
                    route.rows, N, K, form, dtype_code(a.dtype), _stream())
         return out
 
-    def moe_expert_gate_up(self, xs, gate, up, route: MoeRoute) -> torch.Tensor:
-        """silu(xs Wg[e]^T) * (xs Wu[e]^T) over the sorted rows, e the row's expert."""
+    def _moe_gemm_tcgen05(self, a, w, route: MoeRoute, swiglu: bool) -> torch.Tensor:
+        E, N, K = w.shape
+        out = torch.empty((route.rows, N // 2 if swiglu else N), dtype=a.dtype, device=a.device)
+        self._call("roost_gemm_tcgen05_grouped", _ptr(a), _ptr(w), _ptr(out), _ptr(route.wide_tiles), route.max_wide_tiles, route.rows, E, N, K,
+                   1 if swiglu else 0, _stream())
+        return out
+
+    def moe_expert_gate_up(self, xs, gate, up, route: MoeRoute, gate_up: torch.Tensor | None = None) -> torch.Tensor:
+        """silu(xs Wg[e]^T) * (xs Wu[e]^T) over the sorted rows, e the row's expert. ``gate_up`` [experts, 2 ff, k]: the
+        same weights with an expert's gate and up rows interleaved in blocks of 128, the layout in which the tcgen05
+        product applies the activation to its accumulator; steps of many rows run it."""
+        if gate_up is not None and route.wide_tiles is not None and xs.dtype == torch.bfloat16 and xs.shape[1] % 8 == 0:
+            _need(xs, "xs"); _need(gate_up, "gate_up", torch.bfloat16)
+            return self._moe_gemm_tcgen05(xs, gate_up, route, True)
         return self._moe_gemm(xs, gate, up, route)
 
     def moe_expert_down(self, act, down, route: MoeRoute) -> torch.Tensor:
+        if route.wide_tiles is not None and act.dtype == torch.bfloat16 and act.shape[1] % 8 == 0 and down.shape[1] % 8 == 0:
+            _need(act, "act"); _need(down, "down", torch.bfloat16)
+            return self._moe_gemm_tcgen05(act, down, route, False)
         return self._moe_gemm(act, down, None, route)
 
     def moe_combine(self, ys: torch.Tensor, route: MoeRoute, shared: torch.Tensor | None = None) -> torch.Tensor:

@@ -39,6 +39,12 @@ class RoutedMlp(FeedForward):
         self.rt = runtime
         self.router: torch.Tensor | None = None
         self.gate = self.up = self.down = None       # [experts, ff, hidden], [experts, ff, hidden], [experts, hidden, ff]
+        # bfloat16 with an expert size that is a multiple of 128: a second copy of gate and up with an expert's rows interleaved
+        # in blocks of 128, the layout in which the tcgen05 product of steps of many rows applies SiLU(gate) * up to its
+        # accumulator (the copy costs the experts' gate and up weights once more in memory)
+        self.gate_up: torch.Tensor | None = None
+        self.interleave = 128 if (not runtime.full_precision and s.expert_intermediate % 128 == 0 and s.hidden % 8 == 0
+                                  and hasattr(runtime.kernels, "_moe_gemm_tcgen05")) else 0
         self.shared = (GatedMlp(GatedMlpSpec(hidden=s.hidden, intermediate=s.shared_intermediate, activation=s.activation), runtime)
                        if s.shared_intermediate else None)
 
@@ -60,6 +66,9 @@ class RoutedMlp(FeedForward):
         self.gate = params["gate"].to(dt).reshape(E, F, H).contiguous()
         self.up = params["up"].to(dt).reshape(E, F, H).contiguous()
         self.down = params["down"].to(dt).reshape(E, H, F).contiguous()
+        if self.interleave:
+            b = self.interleave
+            self.gate_up = torch.stack([self.gate.reshape(E, F // b, b, H), self.up.reshape(E, F // b, b, H)], dim=2).reshape(E, 2 * F, H).contiguous()
         if self.shared is not None:
             self.shared.load({"gate_up": params["shared_gate_up"], "down": params["shared_down"]})
 
@@ -68,7 +77,8 @@ class RoutedMlp(FeedForward):
         logits = k.moe_router_logits(x, self.router)                            # 32-bit sums, whatever the activation dtype
         route = k.moe_route(logits, s.top)
         xs = k.moe_gather_scale(x, route)                                       # [T * top, hidden]: score * row, sorted by expert
-        act = k.moe_expert_gate_up(xs, self.gate, self.up, route)               # [T * top, ff]
+        act = (k.moe_expert_gate_up(xs, self.gate, self.up, route, self.gate_up) if self.gate_up is not None
+               else k.moe_expert_gate_up(xs, self.gate, self.up, route))       # [T * top, ff]
         ys = k.moe_expert_down(act, self.down, route)                           # [T * top, hidden]
         shared = self.shared(x, batch) if self.shared is not None else None
         return k.moe_combine(ys, route, shared)

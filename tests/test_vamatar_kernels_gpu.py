@@ -200,6 +200,38 @@ def test_routing_chooses_the_largest_scores_and_sorts_the_pairs_by_expert(kernel
     close(outs[1], want, dtype, "experts, a warp an output", bf16=4e-2)
 
 
+def test_experts_on_tcgen05_for_steps_of_many_rows(kernels):
+    """1,230 sorted rows over 9 experts of unequal load (one expert gets no row at all): the grouped tcgen05 product with the
+    activation on its accumulator, and the down product, against the tiles on mma.sync and against the plain formula."""
+    from roost_b200.kernels.library import MOE_TCGEN05_MIN_ROWS
+    T, E, top, hidden, ff = 410, 9, 3, 192, 256
+    g = torch.Generator().manual_seed(12)
+    logits = torch.randn(T, E, generator=g) * 2
+    logits[:, 4] = -50.0                                    # nobody chooses expert 4
+    logits[:200, 7] += 6.0                                  # and many choose expert 7: several tiles of one expert
+    route = kernels.moe_route(logits.cuda(), top)
+    assert T * top >= MOE_TCGEN05_MIN_ROWS and route.wide_tiles is not None
+    x = torch.randn(T, hidden, generator=g).to(torch.bfloat16).cuda()
+    wg = (torch.randn(E, ff, hidden, generator=g) * 0.15).to(torch.bfloat16).cuda()
+    wu = (torch.randn(E, ff, hidden, generator=g) * 0.15).to(torch.bfloat16).cuda()
+    wd = (torch.randn(E, hidden, ff, generator=g) * 0.15).to(torch.bfloat16).cuda()
+    gate_up = torch.stack([wg.reshape(E, ff // 128, 128, hidden), wu.reshape(E, ff // 128, 128, hidden)], dim=2).reshape(E, 2 * ff, hidden).contiguous()
+    xs = kernels.moe_gather_scale(x, route)
+    act_tc = kernels.moe_expert_gate_up(xs, wg, wu, route, gate_up)
+    act_mma = kernels._moe_gemm(xs, wg, wu, route)
+    assert H.scaled_error(act_tc.float(), act_mma.double().cpu()) < 2e-2
+    y_tc = kernels.moe_expert_down(act_mma, wd, route)
+    y_mma = kernels._moe_gemm(act_mma, wd, None, route)
+    assert H.scaled_error(y_tc.float(), y_mma.double().cpu()) < 2e-2
+    kernels.check_device_status()
+    expert, xs_c = route.expert.cpu(), xs.double().cpu()
+    for row in (0, 1, 127, 128, 129, 700, T * top - 1):
+        e = int(expert[row])
+        w = {"gate": wg[e].double().cpu(), "up": wu[e].double().cpu(), "down": wd[e].double().cpu()}
+        gv, uv = xs_c[row] @ w["gate"].T, xs_c[row] @ w["up"].T
+        assert H.scaled_error(act_tc[row].float(), P.silu(gv) * uv) < 2e-2, row
+
+
 @pytest.mark.parametrize("state,vdim", [(100, 24), (200, 40), (3, 128)])
 def test_the_recurrence_at_sizes_of_every_register_class(tmp_path, state, vdim):
     cfg = VM.config([(VM.mamba(heads=2, vdim=vdim, state=state, groups=2, conv=4, norm_groups=1), None)], width=48, vocab=31, cap=None)
