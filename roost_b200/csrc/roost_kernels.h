@@ -320,9 +320,11 @@ int roost_gemm_tcgen05_grouped(const void* a, const void* w, void* out, const in
                                int n, int k, int swiglu, roost_stream_t stream);
 int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
                            roost_stream_t stream);
-/* out[row, :] = a[row, :] w1[e]^T (w2 null) or silu(a w1[e]^T) * (a w2[e]^T), e the row's expert; w: [experts, n, k]. */
+/* out[row, :] = a[row, :] w1[e]^T (w2 null) or silu(a w1[e]^T) * (a w2[e]^T), e the row's expert; w: [experts, n, k]. With
+ * block > 0 the gated form's weights are one tensor, w1 = [experts, 2 n, k], an expert's rows interleaved in blocks of
+ * `block` gate rows then their `block` up rows (w2: any non-null value). */
 int roost_moe_expert_gemm(const void* a, const void* w1, const void* w2, void* out, const int32_t* tiles, int max_tiles,
-                          const int32_t* expert_of, int rows, int n, int k, int form, int dtype, roost_stream_t stream);
+                          const int32_t* expert_of, int rows, int n, int k, int form, int block, int dtype, roost_stream_t stream);
 int roost_moe_combine(const void* ys, const int32_t* inverse, const void* shared, void* out, int tokens, int hidden, int top, int dtype,
                       roost_stream_t stream);
 

@@ -164,11 +164,22 @@ __global__ void moe_gather_scale_kernel(const T* __restrict__ x, T* __restrict__
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[(size_t)row * hidden + i] = from_float<T>(w * to_float(src[i]));
 }
 
+// Gate and up weights come either as two tensors [experts, N, K] (block 0) or as one [experts, 2 N, K] in which an expert's rows
+// are interleaved in blocks of `block` gate rows followed by their `block` up rows (the layout of the tcgen05 product's
+// activation epilogue): output n's gate row is then (n / block) * 2 * block + n % block and its up row `block` rows on.
+template <typename T>
+__device__ __forceinline__ const T* moe_expert_base(const T* w, int e, int N, int K, int block) {
+  return w + (size_t)e * (block ? 2 : 1) * N * K;
+}
+__device__ __forceinline__ size_t moe_weight_row(int n, int block) {
+  return block ? (size_t)(n / block) * 2 * block + n % block : (size_t)n;
+}
+
 // Tiles of 64 sorted rows x 64 outputs of the tile's expert; k in steps of 16. GATED: two weights share the rows and the output
 // is silu(a Wg^T) * (a Wu^T).
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
-                                                           T* __restrict__ out, const int32_t* __restrict__ tiles, int N, int K) {
+                                                           T* __restrict__ out, const int32_t* __restrict__ tiles, int N, int K, int block) {
   constexpr int BM = kMoeTile, BN = 64, BK = 16;
   __shared__ float as[BK][BM + 1];
   __shared__ float ws1[BK][BN + 1];
@@ -179,8 +190,8 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
   if (e < 0) return;
   const int m0 = tiles[3 * blockIdx.y + 1], m_end = tiles[3 * blockIdx.y + 2];
   const int n0 = blockIdx.x * BN;
-  const T* wa = w1 + (size_t)e * N * K;
-  const T* wb = GATED ? w2 + (size_t)e * N * K : nullptr;
+  const T* wa = moe_expert_base(w1, e, N, K, block);
+  const T* wb = GATED ? (block ? wa + (size_t)block * K : w2 + (size_t)e * N * K) : nullptr;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   float acc1[4][4], acc2[GATED ? 4 : 1][4];
 #pragma unroll
@@ -197,8 +208,9 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
       const int row = idx >> 4, col = idx & 15;
       const int k = k0 + col, m = m0 + row, n = n0 + row;
       as[col][row] = (m < m_end && k < K) ? to_float(a[(size_t)m * K + k]) : 0.f;
-      ws1[col][row] = (n < N && k < K) ? to_float(wa[(size_t)n * K + k]) : 0.f;
-      if (GATED) ws2[col][row] = (n < N && k < K) ? to_float(wb[(size_t)n * K + k]) : 0.f;
+      const size_t wr = moe_weight_row(n, block);
+      ws1[col][row] = (n < N && k < K) ? to_float(wa[wr * K + k]) : 0.f;
+      if (GATED) ws2[col][row] = (n < N && k < K) ? to_float(wb[wr * K + k]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -255,7 +267,7 @@ constexpr int moe_tc_stage_elems(bool gated) { return (kMoeTile + (gated ? 2 : 1
 template <bool GATED>
 __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w1,
                                                               const __nv_bfloat16* __restrict__ w2, __nv_bfloat16* __restrict__ out,
-                                                              const int32_t* __restrict__ tiles, int N, int K) {
+                                                              const int32_t* __restrict__ tiles, int N, int K, int block) {
   using namespace nvcuda;
   constexpr int BM = kMoeTile, BN = kMoeTcBN, BK = kMoeTcBK, LD = kMoeTcLD, STAGE = moe_tc_stage_elems(GATED);
   extern __shared__ __align__(128) unsigned char raw[];
@@ -266,8 +278,8 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
   if (e < 0) return;
   const int m0 = tiles[3 * blockIdx.y + 1], m_end = tiles[3 * blockIdx.y + 2];
   const int n0 = blockIdx.x * BN;
-  const __nv_bfloat16* wa = w1 + (size_t)e * N * K;
-  const __nv_bfloat16* wb = GATED ? w2 + (size_t)e * N * K : nullptr;
+  const __nv_bfloat16* wa = moe_expert_base(w1, e, N, K, block);
+  const __nv_bfloat16* wb = GATED ? (block ? wa + (size_t)block * K : w2 + (size_t)e * N * K) : nullptr;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   auto fill = [&](int k0, int st) {
     __nv_bfloat16* As = stages + (size_t)st * STAGE;
@@ -280,8 +292,8 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
         const __nv_bfloat16* src = nullptr;
         if (k < K) {
           if (row < BM) src = m0 + row < m_end ? a + (size_t)(m0 + row) * K + k : nullptr;
-          else if (row < BM + BN) src = n0 + row - BM < N ? wa + (size_t)(n0 + row - BM) * K + k : nullptr;
-          else src = n0 + row - BM - BN < N ? wb + (size_t)(n0 + row - BM - BN) * K + k : nullptr;
+          else if (row < BM + BN) src = n0 + row - BM < N ? wa + moe_weight_row(n0 + row - BM, block) * K + k : nullptr;
+          else src = n0 + row - BM - BN < N ? wb + moe_weight_row(n0 + row - BM - BN, block) * K + k : nullptr;
         }
         if (src) moe_cp16(dst, src);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
@@ -367,7 +379,7 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
 // Few rows: a block per sorted row and 8 outputs, a warp an output; lanes stride over k.
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
-                                                          T* __restrict__ out, const int32_t* __restrict__ expert_of, int N, int K) {
+                                                          T* __restrict__ out, const int32_t* __restrict__ expert_of, int N, int K, int block) {
   constexpr int V = Vec<T>::N;
   pdl_launch_dependents();
   const int row = blockIdx.x;
@@ -377,8 +389,8 @@ __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__
   if (n >= N) return;
   const int e = expert_of[row];
   const T* ar = a + (size_t)row * K;
-  const T* wr1 = w1 + ((size_t)e * N + n) * K;
-  const T* wr2 = GATED ? w2 + ((size_t)e * N + n) * K : nullptr;
+  const T* wr1 = moe_expert_base(w1, e, N, K, block) + moe_weight_row(n, block) * K;
+  const T* wr2 = GATED ? (block ? wr1 + (size_t)block * K : w2 + ((size_t)e * N + n) * K) : nullptr;
   float s1 = 0.f, s2 = 0.f;
   if (K % V == 0 && ((uintptr_t)ar % 16 == 0) && ((uintptr_t)wr1 % 16 == 0) && (!GATED || (uintptr_t)wr2 % 16 == 0)) {
     for (int k = lane * V; k < K; k += 32 * V) {
@@ -476,9 +488,13 @@ extern "C" int roost_moe_gather_scale(const void* x, void* xs, const int32_t* to
 }
 
 // form 0: tiles of rows (tiles: the route's list of max_tiles entries); form 1: a warp an output (expert_of: a sorted row's expert).
+// block > 0: the gated product's weights are one tensor, w1 = [experts, 2 n, k] with gate and up rows interleaved in blocks of
+// `block` (w2 is then only a flag: any non-null value).
 extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* w2, void* out, const int32_t* tiles, int max_tiles,
-                                     const int32_t* expert_of, int rows, int n, int k, int form, int dtype, roost_stream_t stream) {
+                                     const int32_t* expert_of, int rows, int n, int k, int form, int block, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && n > 0 && k > 0 && (form == 0 || form == 1), "moe_expert_gemm: sizes do not fit");
+  ROOST_REQUIRE(block >= 0 && (block == 0 || (w2 != nullptr && n % block == 0)), "moe_expert_gemm: an interleave block must divide n and belongs to the gated form");
+  if (block) w2 = w1;
   if (rows == 0) return ROOST_OK;
   cudaStream_t s = (cudaStream_t)stream;
   if (form == 0) {
@@ -491,23 +507,23 @@ extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* 
       const size_t smem = (size_t)kMoeTcStages * moe_tc_stage_elems(w2 != nullptr) * sizeof(B);
       if (w2) {
         cudaFuncSetAttribute(moe_tile_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_kernel(moe_tile_gemm_tc_kernel<true>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+        launch_kernel(moe_tile_gemm_tc_kernel<true>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k, block);
       } else {
         cudaFuncSetAttribute(moe_tile_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_kernel(moe_tile_gemm_tc_kernel<false>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k);
+        launch_kernel(moe_tile_gemm_tc_kernel<false>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k, block);
       }
       return check_launch("moe_expert_gemm");
     }
     ROOST_DISPATCH_DTYPE(dtype, T, {
-      if (w2) launch_kernel(moe_tile_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k);
-      else launch_kernel(moe_tile_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k);
+      if (w2) launch_kernel(moe_tile_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k, block);
+      else launch_kernel(moe_tile_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k, block);
     });
   } else {
     dim3 grid(rows, (n + 7) / 8);
     if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_expert_gemm: too many outputs");
     ROOST_DISPATCH_DTYPE(dtype, T, {
-      if (w2) launch_kernel(moe_row_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k);
-      else launch_kernel(moe_row_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k);
+      if (w2) launch_kernel(moe_row_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k, block);
+      else launch_kernel(moe_row_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k, block);
     });
   }
   return check_launch("moe_expert_gemm");

@@ -129,7 +129,7 @@ _SIGNATURES = {
                         c_void_p, c_void_p, c_void_p],
     "roost_gemm_tcgen05_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_gather_scale": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_argmax_split": [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -682,15 +682,19 @@ class KernelLibrary:
                    _stream())
         return xs
 
-    def _moe_gemm(self, a, w1, w2, route: MoeRoute) -> torch.Tensor:
+    def _moe_gemm(self, a, w1, w2, route: MoeRoute, block: int = 0) -> torch.Tensor:
+        """The experts' product on tiles of rows or a warp an output. ``block`` > 0: ``w1`` is [experts, 2 n, k] with gate and
+        up rows interleaved in blocks of ``block`` and ``w2`` is not looked at."""
         _need(a, "a"); _need(w1, "w1", a.dtype)
         E, N, K = w1.shape
-        if a.shape != (route.rows, K) or (w2 is not None and w2.shape != w1.shape):
+        if block:
+            N, w2 = N // 2, w1
+        if a.shape != (route.rows, K) or (w2 is not None and not block and w2.shape != w1.shape):
             raise KernelError(f"moe_expert_gemm: rows {tuple(a.shape)} against weights {tuple(w1.shape)}")
         form = 1 if (a.dtype == torch.bfloat16 and route.rows <= MOE_ROW_FORM_MAX_ROWS) else 0
         out = torch.empty((route.rows, N), dtype=a.dtype, device=a.device)
         self._call("roost_moe_expert_gemm", _ptr(a), _ptr(w1), _ptr(w2), _ptr(out), _ptr(route.tiles), route.max_tiles, _ptr(route.expert),
-                   route.rows, N, K, form, dtype_code(a.dtype), _stream())
+                   route.rows, N, K, form, block, dtype_code(a.dtype), _stream())
         return out
 
     def _moe_gemm_tcgen05(self, a, w, route: MoeRoute, swiglu: bool) -> torch.Tensor:
@@ -701,13 +705,16 @@ class KernelLibrary:
         return out
 
     def moe_expert_gate_up(self, xs, gate, up, route: MoeRoute, gate_up: torch.Tensor | None = None) -> torch.Tensor:
-        """silu(xs Wg[e]^T) * (xs Wu[e]^T) over the sorted rows, e the row's expert. ``gate_up`` [experts, 2 ff, k]: the
-        same weights with an expert's gate and up rows interleaved in blocks of 128, the layout in which the tcgen05
-        product applies the activation to its accumulator; steps of many rows run it."""
-        if gate_up is not None and route.wide_tiles is not None and xs.dtype == torch.bfloat16 and xs.shape[1] % 8 == 0:
+        """silu(xs Wg[e]^T) * (xs Wu[e]^T) over the sorted rows, e the row's expert. The weights come as ``gate`` and ``up``
+        [experts, ff, k], or as ``gate_up`` [experts, 2 ff, k] with an expert's gate and up rows interleaved in blocks of
+        128: the layout in which the tcgen05 product of steps of many rows applies the activation to its accumulator, and
+        which the other forms read as well."""
+        if gate_up is None:
+            return self._moe_gemm(xs, gate, up, route)
+        if route.wide_tiles is not None and xs.dtype == torch.bfloat16 and xs.shape[1] % 8 == 0:
             _need(xs, "xs"); _need(gate_up, "gate_up", torch.bfloat16)
             return self._moe_gemm_tcgen05(xs, gate_up, route, True)
-        return self._moe_gemm(xs, gate, up, route)
+        return self._moe_gemm(xs, gate_up, None, route, block=128)
 
     def moe_expert_down(self, act, down, route: MoeRoute) -> torch.Tensor:
         if route.wide_tiles is not None and act.dtype == torch.bfloat16 and act.shape[1] % 8 == 0 and down.shape[1] % 8 == 0:

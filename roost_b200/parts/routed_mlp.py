@@ -39,9 +39,9 @@ class RoutedMlp(FeedForward):
         self.rt = runtime
         self.router: torch.Tensor | None = None
         self.gate = self.up = self.down = None       # [experts, ff, hidden], [experts, ff, hidden], [experts, hidden, ff]
-        # bfloat16 with an expert size that is a multiple of 128: a second copy of gate and up with an expert's rows interleaved
-        # in blocks of 128, the layout in which the tcgen05 product of steps of many rows applies SiLU(gate) * up to its
-        # accumulator (the copy costs the experts' gate and up weights once more in memory)
+        # bfloat16 with an expert size that is a multiple of 128: gate and up are kept as one tensor with an expert's rows
+        # interleaved in blocks of 128, the layout in which the tcgen05 product of steps of many rows applies SiLU(gate) * up
+        # to its accumulator; the products of fewer rows read the same tensor
         self.gate_up: torch.Tensor | None = None
         self.interleave = 128 if (not runtime.full_precision and s.expert_intermediate % 128 == 0 and s.hidden % 8 == 0
                                   and hasattr(runtime.kernels, "_moe_gemm_tcgen05")) else 0
@@ -69,6 +69,7 @@ class RoutedMlp(FeedForward):
         if self.interleave:
             b = self.interleave
             self.gate_up = torch.stack([self.gate.reshape(E, F // b, b, H), self.up.reshape(E, F // b, b, H)], dim=2).reshape(E, 2 * F, H).contiguous()
+            self.gate = self.up = None
         if self.shared is not None:
             self.shared.load({"gate_up": params["shared_gate_up"], "down": params["shared_down"]})
 

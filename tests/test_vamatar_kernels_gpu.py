@@ -184,10 +184,10 @@ def test_routing_chooses_the_largest_scores_and_sorts_the_pairs_by_expert(kernel
     for form in (0, 1):
         a = torch.empty(T * top, ff, dtype=dtype, device="cuda")
         kernels._call("roost_moe_expert_gemm", xs.data_ptr(), wg.data_ptr(), wu.data_ptr(), a.data_ptr(), route.tiles.data_ptr(), route.max_tiles,
-                      route.expert.data_ptr(), T * top, ff, hidden, form, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
+                      route.expert.data_ptr(), T * top, ff, hidden, form, 0, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
         y = torch.empty(T * top, hidden, dtype=dtype, device="cuda")
         kernels._call("roost_moe_expert_gemm", a.data_ptr(), wd.data_ptr(), None, y.data_ptr(), route.tiles.data_ptr(), route.max_tiles,
-                      route.expert.data_ptr(), T * top, hidden, ff, form, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
+                      route.expert.data_ptr(), T * top, hidden, ff, form, 0, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
         outs.append(kernels.moe_combine(y, route, shared))
     want = shared.double().cpu().clone()
     xd = x.double().cpu()
@@ -220,6 +220,13 @@ def test_experts_on_tcgen05_for_steps_of_many_rows(kernels):
     act_tc = kernels.moe_expert_gate_up(xs, wg, wu, route, gate_up)
     act_mma = kernels._moe_gemm(xs, wg, wu, route)
     assert H.scaled_error(act_tc.float(), act_mma.double().cpu()) < 2e-2
+    # the interleaved tensor read by the other forms: tiles on mma.sync, tiles on FFMA, a warp an output (few rows)
+    assert torch.equal(kernels._moe_gemm(xs, gate_up, None, route, block=128), act_mma)
+    few = kernels.moe_route(logits[:10].cuda(), top)
+    xs_few = kernels.moe_gather_scale(x[:10], few)
+    assert H.scaled_error(kernels._moe_gemm(xs_few, gate_up, None, few, block=128).float(), kernels._moe_gemm(xs_few, wg, wu, few).double().cpu()) < 1e-6
+    f32 = lambda t: t.float()
+    assert H.scaled_error(kernels._moe_gemm(f32(xs_few), f32(gate_up), None, few, block=128), kernels._moe_gemm(f32(xs_few), f32(wg), f32(wu), few).double().cpu()) < 1e-6
     y_tc = kernels.moe_expert_down(act_mma, wd, route)
     y_mma = kernels._moe_gemm(act_mma, wd, None, route)
     assert H.scaled_error(y_tc.float(), y_mma.double().cpu()) < 2e-2
