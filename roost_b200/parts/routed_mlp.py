@@ -38,6 +38,10 @@ class RoutedMlp(FeedForward):
         self.spec = s
         self.rt = runtime
         self.router: torch.Tensor | None = None
+        # steps of many tokens in bfloat16 take the router's logits from the library product with a float32 output (the same
+        # 32-bit sums of bfloat16 products, on the tensor cores); fewer tokens and float32 run a warp a (token, expert)
+        self.router_product = Linear(runtime, s.experts, s.hidden)
+        self.router_product_min_rows = 256
         self.gate = self.up = self.down = None       # [experts, ff, hidden], [experts, ff, hidden], [experts, hidden, ff]
         # bfloat16 with an expert size that is a multiple of 128: gate and up are kept as one tensor with an expert's rows
         # interleaved in blocks of 128, the layout in which the tcgen05 product of steps of many rows applies SiLU(gate) * up
@@ -63,6 +67,7 @@ class RoutedMlp(FeedForward):
         s, dt = self.spec, self.rt.dtype
         E, F, H = s.experts, s.expert_intermediate, s.hidden
         self.router = params["router"].to(dt).contiguous()
+        self.router_product.weight = self.router
         self.gate = params["gate"].to(dt).reshape(E, F, H).contiguous()
         self.up = params["up"].to(dt).reshape(E, F, H).contiguous()
         self.down = params["down"].to(dt).reshape(E, H, F).contiguous()
@@ -75,7 +80,10 @@ class RoutedMlp(FeedForward):
 
     def __call__(self, x, batch=None):
         s, k = self.spec, self.rt.kernels
-        logits = k.moe_router_logits(x, self.router)                            # 32-bit sums, whatever the activation dtype
+        if not self.rt.full_precision and x.shape[0] >= self.router_product_min_rows and x.is_contiguous():
+            logits = self.router_product(x, out_dtype=torch.float32)
+        else:
+            logits = k.moe_router_logits(x, self.router)                        # 32-bit sums, whatever the activation dtype
         route = k.moe_route(logits, s.top)
         xs = k.moe_gather_scale(x, route)                                       # [T * top, hidden]: score * row, sorted by expert
         act = (k.moe_expert_gate_up(xs, self.gate, self.up, route, self.gate_up) if self.gate_up is not None
