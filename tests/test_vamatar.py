@@ -214,6 +214,26 @@ def test_long_decoding_past_every_window_and_many_pages(model, backend):
     run.check("r", ids, weights, f"{name} long decoding")
 
 
+LONG = VM.config([(VM.latent(heads=4, dim=16, rot_dim=8, vdim=8, kv_rank=32, window=80, base=10000.0), VM.moe(experts=5, top=2, ff=128, shared=40)),
+                  (VM.mamba(heads=2, vdim=16, state=16, groups=1, conv=4, norm_groups=1), VM.moe(experts=3, top=2, ff=256, shared=0))],
+                 width=72, vocab=83)
+
+
+def test_a_long_prompt_takes_the_forms_of_steps_of_many_rows(tmp_path_factory, backend):
+    """600 tokens in one step and then 2 + 1: on the device in bfloat16 the experts' products run on the grouped tcgen05
+    kernel (1,200 sorted rows, an expert size that is a multiple of 128, a width of 72 that is no multiple of its 64-wide
+    k blocks), the attention on the tensor cores and the recurrence in chunks; the other backends take their own forms of
+    the same step."""
+    folder, cfg, weights = model_dir(tmp_path_factory, "long", LONG, seed=21)
+    run = Run(folder, cfg, backend, page_size=16, num_pages=48)
+    ids = ids_for(cfg, 603, seed=8)
+    run.step([("r", ids[:600])])
+    run.step([("r", ids[600:602])])
+    run.step([("r", ids[602:])])
+    run.finish("r")
+    run.check("r", ids, weights, "long prompt")
+
+
 # ------------------------------------------------------------------------------------------------ keys that must (not) be seen
 WINDOW = 9
 EDGE = VM.config([(VM.latent(heads=2, dim=8, rot_dim=4, vdim=6, kv_rank=10, window=WINDOW), VM.dense(ff=20)),
