@@ -85,14 +85,14 @@ class Run:
     def finish(self, rid):
         self.ex.finish(rid)
 
-    def check(self, rid, ids, weights, what, upto=None):
+    def check(self, rid, ids, weights, what, bf16_bounds=(BF16_WORST, BF16_RMS), slack=ROUTE_SLACK, f32_bounds=(F32_WORST, F32_RMS)):
         got = torch.cat(self.logits.pop(rid))
         forced = {layer: torch.cat(v) for layer, v in self.forced.pop(rid, {}).items()} if self.record else None
         n = got.shape[0]
-        want = P.forward(self.cfg, weights, list(ids[:n]), forced=forced, slack=ROUTE_SLACK)
+        want = P.forward(self.cfg, weights, list(ids[:n]), forced=forced, slack=slack)
         err, rms = H.scaled_error(got, want), H.rms_error(got, want)
         print(f"MEASURED {what} {self.dtype}: worst scaled error {err:.3e}, rms error {rms:.3e}")
-        worst, bound = (F32_WORST, F32_RMS) if self.dtype == torch.float32 else (BF16_WORST, BF16_RMS)
+        worst, bound = f32_bounds if self.dtype == torch.float32 else bf16_bounds
         assert err < worst and rms < bound, f"{what}: worst scaled error {err}, rms error {rms}"
         return got, want
 

@@ -126,7 +126,14 @@ def test_latent_attention_on_the_tensor_cores_against_the_plain_sum(kernels, ran
         tables.append(mine)
     pool = pool.to(torch.bfloat16).cuda()
     T = sum(n for _, n in spans)
-    q_latent = torch.randn(heads, T, rank, generator=g).to(torch.bfloat16).cuda()
+    q_latent = torch.randn(heads, T, rank, generator=g)
+    if window:
+        # two queries of the first request made to score one key far above the rest: the oldest key its window keeps (position
+        # 100 sees 64..100), and the first key its window has dropped (position 110 sees 74..110, not 73); a window one off
+        # turns either result into another
+        q_latent[:, 40] = 2.0 * entries[0][100 - window + 1, :rank]
+        q_latent[:, 50] = 2.0 * entries[0][110 - window, :rank]
+    q_latent = q_latent.to(torch.bfloat16).cuda()
     q = torch.randn(T, heads * (nope + rope), generator=g).to(torch.bfloat16).cuda()
     positions = torch.tensor([start + i for start, n in spans for i in range(n)], dtype=torch.int32).cuda()
     token_row = torch.tensor([b for b, (_, n) in enumerate(spans) for _ in range(n)], dtype=torch.int32).cuda()

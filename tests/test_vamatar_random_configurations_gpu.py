@@ -1,0 +1,100 @@
+"""Vamatar models drawn at random (layer order, every size, windows, readers of earlier caches, routing, constants), each run
+through the step function in random portions and batches with pages and slots used again, against the plain implementation.
+The draws here are a sample of a longer run of the same generator (``draw_config`` with other seeds). float32 holds every
+draw to a worst scaled error of 1e-3 and a root mean square of 5e-5 (five recurrences on top of one another bring the worst of
+a hundred thousand logits to 4e-4 at a root mean square of 1e-5; a misplaced key, state or page moves logits by percents). In bfloat16 some draws are ill-conditioned (a group of the recurrence's gated output
+that is nearly zero is divided by its tiny root mean square: at such a token even the float32 engine is a hundred times
+further from the float64 implementation than elsewhere, and the bfloat16 stream is off by a tenth of its size, which then
+routes that token elsewhere), so those runs follow the engine's routing and are held to the median over a request's tokens
+of the per-token error: what they add is that every drawn size finds a bfloat16 kernel that serves it, with the strides and
+alignments it brings, and stays close wherever the model is well-conditioned; faults of indexing show in float32."""
+import random
+
+import pytest
+import torch
+
+from tests import helpers as H
+from tests import vamatar_models as VM
+from tests.plain import vamatar_plain as P
+from tests.test_vamatar import Run
+
+pytestmark = pytest.mark.gpu
+
+
+def draw_config(seed: int) -> dict:
+    rng = random.Random(seed)
+    width = rng.choice([24, 40, 64, 72, 96, 136, 320])
+    layers, owners = [], []          # owners: (layer index, its latent's geometry)
+    for i in range(rng.randint(2, 6)):
+        if rng.random() < 0.5:
+            geometry = None
+            if owners and rng.random() < 0.4:
+                src, geometry = rng.choice(owners)
+            if geometry is None:
+                rot_dim = rng.choice([2, 4, 8, 16, 32])
+                geometry = dict(kv_rank=rng.choice([8, 12, 16, 32, 48, 64, 96]), rot_dim=rot_dim, dims=rng.choice([rot_dim, max(2, rot_dim // 2)]),
+                                base=rng.choice([50.0, 10000.0, 1000000.0]))
+                src = None
+            layer = VM.latent(heads=rng.randint(1, 8), dim=rng.choice([4, 8, 16, 24, 32, 64]), vdim=rng.choice([3, 8, 16, 40, 64]),
+                              window=rng.choice([None, 3, 17, 72, 100]), scale=rng.choice([None, 0.07, 0.2]), kv_from=src, **geometry)
+            if src is None:
+                owners.append((i, geometry))
+        else:
+            heads = rng.choice([1, 2, 4, 6, 8])
+            vdim = rng.choice([4, 8, 16, 48])
+            layer = VM.mamba(heads=heads, vdim=vdim, state=rng.choice([4, 16, 48, 64]), groups=rng.choice([g for g in (1, 2, 3, 4, 8) if heads % g == 0]),
+                             conv=rng.randint(1, 4), norm_groups=rng.choice([n for n in (1, 2, heads) if (heads * vdim) % n == 0]))
+        kind = rng.random()
+        if kind < 0.15:
+            mlp = None
+        elif kind < 0.45:
+            mlp = VM.dense(ff=rng.choice([16, 48, 128]))
+        else:
+            experts = rng.randint(2, 16)
+            mlp = VM.moe(experts=experts, top=rng.randint(1, min(4, experts)), ff=rng.choice([8, 64, 128]), shared=rng.choice([0, 32, 128]))
+        layers.append((layer, mlp))
+    return VM.config(layers, width=width, vocab=rng.randint(50, 500), eps=rng.choice([1e-5, 1e-6]), scale=rng.choice([0.5, 1.0, 2.0]),
+                     cap=rng.choice([None, 15.0, 30.0]))
+
+
+def run_draw(tmp_path, seed: int, dtype) -> None:
+    cfg = draw_config(seed)
+    rng = random.Random(seed * 7 + 1)
+    tensors = VM.draw_tensors(cfg, seed)
+    folder = VM.write_model(tmp_path, cfg, tensors)
+    weights = VM.plain_weights(tensors)
+    page = rng.choice([4, 8, 16])
+    run = Run(folder, cfg, ("gpu", dtype), page_size=page, num_pages=3 * (-(-330 // page)) + 2, slots=3)
+    reqs = {f"q{i}": H.random_ids(rng.choice([1, 2, 7, 40, 131, 300]), cfg["vocab"], seed * 13 + i) for i in range(5)}
+    waiting, live = list(reqs), {}
+    while waiting or live:
+        while waiting and len(live) < 3:
+            live[waiting.pop(0)] = 0
+        entries = []
+        for rid in [r for r in live if rng.random() < 0.8] or [next(iter(live))]:
+            left = len(reqs[rid]) - live[rid]
+            n = 1 if left <= 5 else min(left - 5, rng.choice([2, 3, 9, 33, 64, 200]))
+            entries.append((rid, reqs[rid][live[rid] : live[rid] + n]))
+            live[rid] += n
+        run.step(entries)
+        for rid, _ in entries:
+            if live[rid] == len(reqs[rid]):
+                run.finish(rid)
+                del live[rid]
+    for rid, ids in reqs.items():
+        if dtype == torch.float32:
+            run.check(rid, ids, weights, f"draw {seed} {rid}", f32_bounds=(1e-3, 5e-5))
+            continue
+        got = torch.cat(run.logits.pop(rid)).double()
+        forced = {layer: torch.cat(v) for layer, v in run.forced.pop(rid, {}).items()}
+        want = P.forward(cfg, weights, list(ids), forced=forced, slack=float("inf"))
+        per_token = ((got - want) ** 2).mean(1).sqrt() / (want ** 2).mean().sqrt()
+        assert torch.isfinite(got).all() and float(per_token.median()) < 0.08, (seed, rid, float(per_token.median()))
+    assert run.all_free()
+    run.model.rt.kernels.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 5, 8, 13, 21, 34])
+def test_random_configurations_in_random_portions_and_batches(tmp_path, seed, dtype):
+    run_draw(tmp_path, seed, dtype)
