@@ -4,8 +4,8 @@
 // consecutive packed rows, loads their queries [q_latent | q_rot] once, and walks the keys they can see in tiles of 32,
 // copied from the pages by cp.async into two buffers. Per tile a warp (16 rows) forms S = Q K^T with mma.sync m16n8k16
 // (32-bit accumulators), scales and masks it per row (a row's window is its own token's), keeps the running maximum and
-// denominator in 32-bit, and adds P V with V = the first `rank` numbers of the same tile, P rounded to bfloat16 as the
-// operand. The sums of a row live in registers: `NT` column tiles of 8 a warp; beyond 256 latent numbers two warps share a
+// denominator in 32-bit, and adds P V with V = the first `rank` numbers of the same tile; a weight enters that product as two bfloat16 operands
+// (its rounding and the remainder), so that the 32-bit weights are used to 16 bits and not to 8. The sums of a row live in registers: `NT` column tiles of 8 a warp; beyond 256 latent numbers two warps share a
 // row group, each with half of the columns and its own copy of S. A block finds its request by walking q_indptr, so the
 // kernel needs no list from the host; blocks beyond the step's tiles leave at once.
 #include "common.cuh"
@@ -182,15 +182,18 @@ __global__ void __launch_bounds__(128 * RC) latent_attention_tc_kernel(
     m_a = mn_a;
     m_b = mn_b;
     float sum_a = 0.f, sum_b = 0.f;
-    uint32_t p[2][4];
+    uint32_t p[2][4], p_low[2][4];      // a weight as two bfloat16 operands, its rounding and what the rounding left: 16 bits of it
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       const float p0 = expf(s[nt][0] - base_a), p1 = expf(s[nt][1] - base_a);
       const float p2 = expf(s[nt][2] - base_b), p3 = expf(s[nt][3] - base_b);
       sum_a += p0 + p1;
       sum_b += p2 + p3;
-      p[nt >> 1][(nt & 1) * 2] = pack_bf16(p0, p1);
-      p[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2, p3);
+      const uint32_t hi_a = pack_bf16(p0, p1), hi_b = pack_bf16(p2, p3);
+      p[nt >> 1][(nt & 1) * 2] = hi_a;
+      p[nt >> 1][(nt & 1) * 2 + 1] = hi_b;
+      p_low[nt >> 1][(nt & 1) * 2] = pack_bf16(p0 - __uint_as_float(hi_a << 16), p1 - __uint_as_float(hi_a & 0xffff0000u));
+      p_low[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p2 - __uint_as_float(hi_b << 16), p3 - __uint_as_float(hi_b & 0xffff0000u));
     }
     l_a = l_a * corr_a + sum_a;
     l_b = l_b * corr_b + sum_b;
@@ -211,7 +214,11 @@ __global__ void __launch_bounds__(128 * RC) latent_attention_tc_kernel(
           uint32_t vb[4];
           ldsm_x4_trans(vb, Kt + (kt * 16 + (lane & 15)) * LD + d0 + (lane >> 4) * 8);
           mma_bf16_16816(o[i], p[kt], vb[0], vb[1]);
-          if (d0 + 8 < rank) mma_bf16_16816(o[i + 1], p[kt], vb[2], vb[3]);
+          mma_bf16_16816(o[i], p_low[kt], vb[0], vb[1]);
+          if (d0 + 8 < rank) {
+            mma_bf16_16816(o[i + 1], p[kt], vb[2], vb[3]);
+            mma_bf16_16816(o[i + 1], p_low[kt], vb[2], vb[3]);
+          }
         }
       }
     }
