@@ -243,8 +243,7 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
       if (n >= N) continue;
       float v = acc1[i][j];
       if (GATED) {
-        const float g = to_float(from_float<T>(v)), up = to_float(from_float<T>(acc2[i][j]));   // the two products, rounded as outputs
-        v = g / (1.0f + expf(-g)) * up;
+        v = v / (1.0f + expf(-v)) * acc2[i][j];     // on the 32-bit sums
       }
       out[(size_t)m * N + n] = from_float<T>(v);
     }
@@ -255,7 +254,7 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
 // tile of 64 sorted rows and 128 outputs, four warps with 64 x 32 each (a fragment of the rows serves two or four products);
 // k in steps of 32 through three stages of shared memory filled by cp.async. Needs k a multiple of 8 (16-byte pieces of whole
 // rows). A warp's accumulators leave through a patch of shared memory of its own, where the gated form applies
-// silu(gate) * up to the two products rounded as outputs.
+// silu(gate) * up to the two 32-bit sums.
 __device__ __forceinline__ void moe_cp16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
@@ -360,9 +359,7 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
         for (int c = 0; c < 8; ++c) {
           v[c] = patch[pr * 20 + pc + c];
           if (GATED) {
-            const float g = __bfloat162float(__float2bfloat16_rn(v[c]));
-            const float up = __bfloat162float(__float2bfloat16_rn(patch[16 * 20 + pr * 20 + pc + c]));
-            v[c] = g / (1.0f + expf(-g)) * up;
+            v[c] = v[c] / (1.0f + expf(-v[c])) * patch[16 * 20 + pr * 20 + pc + c];     // on the 32-bit sums
           }
         }
         __nv_bfloat16* dst = out + (size_t)m * N + n;
@@ -417,8 +414,7 @@ __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__
   if (lane == 0) {
     float v = s1;
     if (GATED) {
-      const float g = to_float(from_float<T>(s1)), up = to_float(from_float<T>(s2));
-      v = g / (1.0f + expf(-g)) * up;
+      v = s1 / (1.0f + expf(-s1)) * s2;     // on the 32-bit sums
     }
     out[(size_t)row * N + n] = from_float<T>(v);
   }
