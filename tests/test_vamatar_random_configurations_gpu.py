@@ -23,7 +23,7 @@ pytestmark = pytest.mark.gpu
 
 def draw_config(seed: int) -> dict:
     rng = random.Random(seed)
-    width = rng.choice([24, 40, 64, 72, 96, 136, 320])
+    width = rng.choice([24, 40, 64, 72, 96, 136, 200])
     layers, owners = [], []          # owners: (layer index, its latent's geometry)
     for i in range(rng.randint(2, 6)):
         if rng.random() < 0.5:
@@ -36,7 +36,7 @@ def draw_config(seed: int) -> dict:
                                 base=rng.choice([50.0, 10000.0, 1000000.0]))
                 src = None
             layer = VM.latent(heads=rng.randint(1, 8), dim=rng.choice([4, 8, 16, 24, 32, 64]), vdim=rng.choice([3, 8, 16, 40, 64]),
-                              window=rng.choice([None, 3, 17, 72, 100]), scale=rng.choice([None, 0.07, 0.2]), kv_from=src, **geometry)
+                              window=rng.choice([None, 3, 17, 56, 100]), scale=rng.choice([None, 0.07, 0.2]), kv_from=src, **geometry)
             if src is None:
                 owners.append((i, geometry))
         else:
