@@ -15,16 +15,19 @@ from dataclasses import dataclass, field
 @dataclass(frozen=True)
 class NormSpec:
     """``rms_norm``: x / sqrt(mean(x^2) + eps) * w. ``layer_norm``: (x - mean) / sqrt(var + eps) * w + b, var the mean squared
-    deviation; it reads a 32-bit stream and writes the activation dtype."""
+    deviation; it reads a 32-bit stream and writes the activation dtype. ``weight_offset``: what is added to the stored
+    weight before it multiplies (1.0 for weights stored around zero)."""
     size: int
     eps: float
     kind: str = "rms_norm"
+    weight_offset: float = 0.0
 
 
 @dataclass(frozen=True)
 class PositionSpec:
     """Position encoding applied inside a mixer. ``rope_neox``: rotation of the first ``rotary_dim``
-    elements of each head, pairs (i, i + rotary_dim/2), frequencies theta^(-2i/rotary_dim)."""
+    elements of each head, pairs (i, i + rotary_dim/2), frequencies theta^(-2i/rotary_dim). ``rope_interleaved``: the same
+    angles with element 2i paired with element 2i + 1."""
     kind: str = "rope_neox"
     rotary_dim: int = 0
     theta: float = 10000.0
@@ -75,6 +78,39 @@ class LatentAttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class SinkAttentionSpec(MixerSpec):
+    """Grouped-query causal attention whose values have a size of their own (``v_dim``) and whose softmax may have a sink:
+    with ``sink`` the denominator is 1 + sum exp(s_j), a key of score 0 that has no value. Queries and keys are rotated
+    (``position``) and then, with ``unit_norm_eps`` set, divided by their root mean square over ``head_dim`` (eps inside the
+    root, no weight). Every earlier key is seen. The cache keeps one entry [key | value] a token and key/value head."""
+    kind: str = "sink_attention"
+    hidden: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    v_dim: int = 0
+    scale: float = 0.0
+    sink: bool = True
+    unit_norm_eps: float | None = None
+    position: PositionSpec | None = None
+
+
+@dataclass(frozen=True)
+class Mamba1Spec(MixerSpec):
+    """The Mamba selective scan. The input projection gives [x | z] of ``inner`` channels each; x passes a causal
+    convolution of ``conv_taps`` taps a channel and SiLU; a projection of x gives [dt (``dt_rank``) | B (``state``) | C
+    (``state``)]; dt = softplus(W_dt dt + bias), one a channel; per channel c and state n S[c, n] <- exp(dt_c A[c, n]) S[c, n] +
+    dt_c x_c B_n with A = -exp(A_log), y_c = sum_n S[c, n] C_n + D_c x_c; y SiLU(z) is projected out. S and the last
+    ``conv_taps`` - 1 inputs of the convolution are kept per request in 32-bit."""
+    kind: str = "mamba1"
+    hidden: int = 0
+    inner: int = 0
+    state: int = 0
+    dt_rank: int = 0
+    conv_taps: int = 4
+
+
+@dataclass(frozen=True)
 class Mamba2Spec(MixerSpec):
     """The Mamba-2 recurrence. The input projection gives [z | x | B | C | dt]; x, B and C pass a causal convolution of
     ``conv_taps`` taps a channel and SiLU; per head (``head_dim`` values, state ``state`` x ``head_dim``, B and C shared by
@@ -99,11 +135,14 @@ class FeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedMlpSpec(FeedForwardSpec):
-    """down(act(x Wg^T) * (x Wu^T)); ``activation`` is the gate's function."""
+    """down(act(x Wg^T) * (x Wu^T)); ``activation`` is the gate's function: "silu", "gelu_tanh" (0.5 g (1 + tanh(sqrt(2/pi)
+    (g + 0.044715 g^3)))), or "clamped_swish": with g = min(gate, limit) and u = clamp(up, -limit, limit) the product is
+    g sigmoid(1.702 g) (u + 1)."""
     kind: str = "gated_mlp"
     hidden: int = 0
     intermediate: int = 0
     activation: str = "silu"
+    limit: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -112,7 +151,11 @@ class RoutedMlpSpec(FeedForwardSpec):
     router scores, and a shared one of ``shared_intermediate`` rows (0: none) that every token uses. ``score``: the
     function that turns router logits into scores ("sigmoid"); ``renormalize``: whether the chosen scores are divided by
     their sum; ``weight_on``: "input" when a chosen expert is given score * x (the sum of expert(score x)), "output" when
-    its output is multiplied."""
+    its output is multiplied. ``score`` "softmax": scores are the softmax of the logits over the experts and the
+    ``identity_experts`` (router outputs beyond the experts, whose output is their input; they have no weights); with
+    ``correction`` a stored vector is added to the scores for the choice only; the weights are the chosen scores times
+    ``route_scale``. ``activation``, ``limit``: as in ``GatedMlpSpec``; ``shared_limit`` is the shared expert's limit;
+    ``shared_gate``: the shared expert's output is multiplied by the sigmoid of one more router-like product a token."""
     kind: str = "routed_mlp"
     hidden: int = 0
     experts: int = 0
@@ -123,6 +166,12 @@ class RoutedMlpSpec(FeedForwardSpec):
     score: str = "sigmoid"
     renormalize: bool = False
     weight_on: str = "input"
+    correction: bool = False
+    route_scale: float = 1.0
+    identity_experts: int = 0
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    shared_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -158,15 +207,28 @@ class CappedHeadSpec(HeadSpec):
 
 
 @dataclass(frozen=True)
+class ConnectionSpec:
+    """How a sublayer reads the residual and writes back to it. ``hyper_connection``: the residual is ``streams`` copies
+    x_1 .. x_S in 32-bit, all equal to the embedding at the start; the sublayer reads u = sum_s in[s] x_s and its output y
+    goes back as x_t <- sum_s mix[s, t] x_s + out[t] y, every stream at once from the old ones; the model's output is the sum
+    of the streams. ``learned`` False: in, mix and out are ones (with one stream: the plain residual sum)."""
+    kind: str = "hyper_connection"
+    streams: int = 1
+    learned: bool = True
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer's parts and their arrangement. ``pre_norm``: h += mixer(norm1(h)); h += ff(norm2(h)), the stream in the
     activation dtype. ``pre_norm_wide``: the same with the stream kept and summed in 32-bit whatever the activation dtype
-    is; its ``feed_forward`` and ``post_mixer_norm`` may be None (a layer that is its mixer only)."""
+    is; its ``feed_forward`` and ``post_mixer_norm`` may be None (a layer that is its mixer only). ``pre_norm_streams``:
+    the same two sublayers over several 32-bit residual streams, read and written through ``connection``."""
     mixer: MixerSpec
     feed_forward: FeedForwardSpec | None
     input_norm: NormSpec
     post_mixer_norm: NormSpec | None
     kind: str = "pre_norm"
+    connection: ConnectionSpec | None = None
 
 
 @dataclass(frozen=True)

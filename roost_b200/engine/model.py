@@ -119,7 +119,10 @@ class Model:
             h, residual = self.blocks[e.block](h, residual, batch, storage.view(owner), write_cache=e.reads_cache_of is None)
         if batch.num_selected == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
-        if residual is None:
+        close = getattr(self.blocks[self.spec.schedule[-1].block], "close", None)
+        if close is not None and residual is not None:      # a block arrangement that ends the residual its own way
+            final = close(h, residual, self.final_norm, batch.selected)
+        elif residual is None:
             final = self.final_norm(h, rows=batch.selected)
         else:
             final, _ = self.final_norm.add_norm(h, residual, rows=batch.selected)

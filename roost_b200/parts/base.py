@@ -30,7 +30,7 @@ class ParamDecl:
     # bfloat16 path; "table": integer tables become int32. In the 32-bit path every float becomes float32.
     role: str = "matrix"
     # how the random-weights mode draws the parameter when the role's default (matrices N(0, std), vectors 1 + N(0, norm_std))
-    # does not suit it: ("normal", mean, std) or ("uniform", low, high)
+    # does not suit it: ("normal", mean, std), ("uniform", low, high) or ("eye_normal", scale, std): scale * identity + N(0, std)
     init: tuple | None = None
 
 
@@ -163,6 +163,11 @@ class Head(Part):
         raise NotImplementedError
 
 
+class Connection(Part):
+    """How a sublayer reads the residual streams and writes its output back (``ConnectionSpec``). Declares its parameters
+    under the scopes "blocks.<i>.mixer_connection" and "blocks.<i>.feed_forward_connection"."""
+
+
 class Block(Part):
     mixer: Mixer
 
@@ -199,6 +204,7 @@ FEED_FORWARDS = _Registry("feed-forward")
 BLOCKS = _Registry("block arrangement")
 EMBEDDINGS = _Registry("embedding")
 HEADS = _Registry("head")
+CONNECTIONS = _Registry("residual connection")
 
 
 def register_norm(kind, cls):
@@ -227,3 +233,7 @@ def register_embedding(kind, cls):
 
 def register_head(kind, cls):
     HEADS.register(kind, cls)
+
+
+def register_connection(kind, cls):
+    CONNECTIONS.register(kind, cls)

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import BlockSpec
-from .base import FEED_FORWARDS, MIXERS, NORMS, Block, Runtime, register_block
+from .base import CONNECTIONS, FEED_FORWARDS, MIXERS, NORMS, Block, Runtime, register_block
 
 
 class PreNormBlock(Block):
@@ -86,5 +86,78 @@ class PreNormWideBlock(Block):
         return self.feed_forward(y, batch), residual
 
 
+class StreamState:
+    """The residual streams between two sublayers: the 32-bit tensor [tokens, streams, width] and the connection whose
+    write-back of the branch output that travels beside it is still to be applied."""
+    __slots__ = ("streams", "pending")
+
+    def __init__(self, streams, pending):
+        self.streams, self.pending = streams, pending
+
+
+class PreNormStreamsBlock(Block):
+    """h += mixer(norm1(h)); h += ff(norm2(h)) over several 32-bit residual streams: every sum is a connection's read, mix
+    and write (``parts/connections.py``). The block hands on its last branch output and the streams it is still to be
+    written to; the next block's first kernel applies that write and makes its own read in one pass. ``close`` does the
+    same for the model's end: the write, the sum of the streams and the final norm of the wanted rows."""
+
+    def __init__(self, spec: BlockSpec, runtime: Runtime):
+        if spec.connection is None:
+            raise ValueError("pre_norm_streams: the block needs a connection")
+        self.spec = spec
+        self.rt = runtime
+        self.input_norm = NORMS.build(spec.input_norm, runtime)
+        self.mixer = MIXERS.build(spec.mixer, runtime)
+        self.mixer_connection = CONNECTIONS.build(spec.connection, runtime)
+        self.feed_forward = self.post_mixer_norm = self.feed_forward_connection = None
+        if spec.feed_forward is not None:
+            if spec.post_mixer_norm is None:
+                raise ValueError("pre_norm_streams: a feed-forward needs the norm before it")
+            self.post_mixer_norm = NORMS.build(spec.post_mixer_norm, runtime)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, runtime)
+            self.feed_forward_connection = CONNECTIONS.build(spec.connection, runtime)
+
+    def sub_parts(self):
+        parts = {"input_norm": self.input_norm, "mixer": self.mixer, "mixer_connection": self.mixer_connection}
+        if self.feed_forward is not None:
+            parts.update({"post_mixer_norm": self.post_mixer_norm, "feed_forward": self.feed_forward,
+                          "feed_forward_connection": self.feed_forward_connection})
+        return parts
+
+    @classmethod
+    def sub_specs(cls, spec: BlockSpec):
+        subs = {"input_norm": (NORMS, spec.input_norm), "mixer": (MIXERS, spec.mixer), "mixer_connection": (CONNECTIONS, spec.connection)}
+        if spec.feed_forward is not None:
+            subs.update({"post_mixer_norm": (NORMS, spec.post_mixer_norm), "feed_forward": (FEED_FORWARDS, spec.feed_forward),
+                         "feed_forward_connection": (CONNECTIONS, spec.connection)})
+        return subs
+
+    def _read(self, h, state, connection, norm, rows=None):
+        """Applies the pending write of ``h`` (if any), then ``connection``'s read (None: the sum of the streams) and ``norm``."""
+        k, S = self.rt.kernels, self.spec.connection.streams
+        if state is None:       # the embedding: every stream starts as a copy of it
+            streams = torch.empty((h.shape[0], S, h.shape[1]), dtype=torch.float32, device=h.device)
+            x = k.stream_step(streams, norm.weight, norm.spec.eps, self.rt.dtype, read=connection.read, init_from=h)
+            return x, streams
+        p = state.pending
+        x = k.stream_step(state.streams, norm.weight, norm.spec.eps, self.rt.dtype, read=None if connection is None else connection.read,
+                          y=h, mix=p.mix, write=p.write, rows=rows)
+        return x, state.streams
+
+    def __call__(self, h, residual, batch, cache, write_cache: bool = True):
+        x, streams = self._read(h, residual, self.mixer_connection, self.input_norm)
+        a = self.mixer(x, batch, cache, write_cache)
+        state = StreamState(streams, self.mixer_connection)
+        if self.feed_forward is None:
+            return a, state
+        y, _ = self._read(a, state, self.feed_forward_connection, self.post_mixer_norm)
+        return self.feed_forward(y, batch), StreamState(streams, self.feed_forward_connection)
+
+    def close(self, h, residual, norm, rows):
+        """The model's end: the last write, the sum of the streams of the wanted rows and ``norm`` of it."""
+        return self._read(h, residual, None, norm, rows=rows)[0]
+
+
+register_block("pre_norm_streams", PreNormStreamsBlock)
 register_block("pre_norm", PreNormBlock)
 register_block("pre_norm_wide", PreNormWideBlock)

@@ -1,6 +1,8 @@
 """The gated feed-forward: down(act(x Wg^T) * (x Wu^T)), gate and up as one product over the row-wise
 concatenation [gate; up] made at load (src/Starlings.Roost.Models.Tiny/RoostTiny.cs:35-36,51-53;
-silu(g) = g / (1 + exp(-g)), src/Starlings.Roost.Ops/CpuOps.cs:355-368)."""
+silu(g) = g / (1 + exp(-g)), src/Starlings.Roost.Ops/CpuOps.cs:355-368). Other gate functions (``GatedMlpSpec.activation``:
+the tanh form of GELU, the clamped swish of routed designs) run the same products with the activation kernel that takes
+the function as an argument; the products that apply SiLU to their own sums serve "silu" only."""
 from __future__ import annotations
 
 from ..config.spec import GatedMlpSpec
@@ -8,12 +10,17 @@ from .base import FeedForward, ParamDecl, Runtime, register_feed_forward
 from .linear import Linear
 
 
+GATE_FUNCTIONS = ("silu", "gelu_tanh", "clamped_swish")
+
+
 class GatedMlp(FeedForward):
     def __init__(self, spec: GatedMlpSpec, runtime: Runtime):
         if spec.hidden <= 0 or spec.intermediate <= 0:
             raise ValueError("gated_mlp: hidden and intermediate must be positive")
-        if spec.activation != "silu":
-            raise ValueError(f"gated_mlp: activation '{spec.activation}' has no kernel (built: silu)")
+        if spec.activation not in GATE_FUNCTIONS:
+            raise ValueError(f"gated_mlp: activation '{spec.activation}' has no kernel (built: {', '.join(GATE_FUNCTIONS)})")
+        if spec.activation == "clamped_swish" and not spec.limit > 0:
+            raise ValueError("gated_mlp: the clamped swish needs a positive limit")
         self.spec = spec
         self.rt = runtime
         self.gate_up = Linear(runtime, 2 * spec.intermediate, spec.hidden)
@@ -24,7 +31,7 @@ class GatedMlp(FeedForward):
         # SiLU kernel, which reads the same layout.
         k = runtime.kernels
         self.interleave = 128 if (not runtime.full_precision and spec.intermediate % 128 == 0 and spec.hidden % 8 == 0
-                                  and hasattr(k, "gemm_tcgen05_swiglu")) else 0
+                                  and spec.activation == "silu" and hasattr(k, "gemm_tcgen05_swiglu")) else 0
         self.fused_min_rows = 256   # below this the 128-row tiles are mostly empty and the library product is faster
         # ... and so it is while the product is small: measured on a B200, the library product followed by the SiLU kernel
         # wins at rows x intermediate x hidden below about 2.5e10 (hidden 1024, intermediate 3072: 12.9 against 19.4 us at
@@ -58,6 +65,8 @@ class GatedMlp(FeedForward):
 
     def __call__(self, x, batch=None):
         k = self.rt.kernels
+        if self.spec.activation != "silu":
+            return self.down(k.gated_act_mul(self.gate_up(x), self.spec.activation, float(self.spec.limit)))
         if (self.interleave and x.shape[0] >= self.fused_min_rows and x.is_contiguous()
                 and float(x.shape[0]) * self.spec.intermediate * self.spec.hidden >= self.fused_min_work):
             return self.down(k.gemm_tcgen05_swiglu(x, self.gate_up.weight))

@@ -23,6 +23,8 @@ class RmsNorm(Norm):
 
     def load(self, params):
         self.weight = params["weight"].contiguous()
+        if self.spec.weight_offset:     # a weight stored around zero: offset + w, formed once in 32-bit
+            self.weight = (self.weight.float() + float(self.spec.weight_offset)).contiguous()
 
     def __call__(self, x: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         return self.rt.kernels.rms_norm(x, self.weight, self.spec.eps, rows)

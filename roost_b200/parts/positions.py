@@ -38,6 +38,8 @@ class RopeNeox(PositionEncoding):
     hand out the same tensor: a step keeps its table of cosines and sines by that tensor, so that the layers of a model,
     each with an encoding of its own, share one table a step."""
 
+    pairing = "halves"
+
     def __init__(self, spec: PositionSpec, runtime: Runtime):
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
             raise ValueError(f"rope_neox: rotary_dim {spec.rotary_dim} must be positive and even")
@@ -55,6 +57,13 @@ class RopeNeox(PositionEncoding):
         return self.inv_freq, self.spec.rotary_dim
 
 
+class RopeInterleaved(RopeNeox):
+    """The same angles as ``rope_neox`` with element 2i paired with element 2i + 1: the pair (u, v) at position p becomes
+    (u cos a - v sin a, v cos a + u sin a), a = p f_i. The pairing is the mixer's kernel's; a mixer that takes this encoding
+    says so (``pairing``)."""
+    pairing = "interleaved"
+
+
 class NoPosition(PositionEncoding):
     def __init__(self, spec: PositionSpec, runtime: Runtime):
         self.spec = spec
@@ -64,4 +73,5 @@ class NoPosition(PositionEncoding):
 
 
 register_position("rope_neox", RopeNeox)
+register_position("rope_interleaved", RopeInterleaved)
 register_position("none", NoPosition)

@@ -64,13 +64,16 @@ def random_tensors(config: dict, seed: int, std: float = 0.02, norm_std: float =
 
 
 def _draw(init: tuple, shape, generator, device) -> torch.Tensor:
-    """A parameter drawn as its declaration asks: ("normal", mean, std) or ("uniform", low, high), in float32."""
+    """A parameter drawn as its declaration asks: ("normal", mean, std), ("uniform", low, high) or ("eye_normal", scale, std)
+    (a square matrix: scale * identity + N(0, std)), in float32."""
     kind, a, b = init
+    if kind == "eye_normal":
+        return a * torch.eye(shape[0], shape[1], dtype=torch.float32, device=device) + b * torch.randn(shape, generator=generator, dtype=torch.float32, device=device)
     if kind == "normal":
         return a + b * torch.randn(shape, generator=generator, dtype=torch.float32, device=device)
     if kind == "uniform":
         return a + (b - a) * torch.rand(shape, generator=generator, dtype=torch.float32, device=device)
-    raise ValueError(f"a parameter asks to be drawn as '{kind}'; known: normal, uniform")
+    raise ValueError(f"a parameter asks to be drawn as '{kind}'; known: normal, uniform, eye_normal")
 
 
 REFERENCE_TINY_SEED = 0x524F4F53540001   # the seed of the reference's dense tiny model (src/Starlings.Roost.Models.Tiny/TinyConfig.cs:63-66)

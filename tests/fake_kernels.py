@@ -216,13 +216,20 @@ class FakeKernels:
     def moe_router_logits(self, x, w):
         return x.float() @ w.float().t()
 
-    def moe_route(self, logits, top):
+    def moe_route(self, logits, top, score="sigmoid", correction=None, scale=1.0, routed=None, real=None):
         from types import SimpleNamespace
-        T, E = logits.shape
-        s = torch.sigmoid(logits)
+        T, C = logits.shape
+        E = C if routed is None else routed
+        if score == "sigmoid":
+            s = torch.sigmoid(logits)
+            choice = logits                          # by logit: the sigmoid saturates in 32-bit
+        else:
+            s = torch.softmax(logits[:, :E].float(), dim=-1)
+            choice = s + (correction.float() if correction is not None else 0.0)
+            s = s * scale
         pairs = []
         for t in range(T):
-            for e in sorted(range(E), key=lambda e: (-float(logits[t, e]), e))[:top]:     # by logit: the sigmoid saturates in 32-bit
+            for e in sorted(range(E), key=lambda e: (-float(choice[t, e]), e))[:top]:
                 pairs.append((e, t, float(s[t, e])))
         order = sorted(range(len(pairs)), key=lambda i: (pairs[i][0], i))
         inverse = torch.zeros(len(pairs), dtype=torch.int32)
@@ -230,22 +237,137 @@ class FakeKernels:
             inverse[i] = dest
         return SimpleNamespace(top=top, token=torch.tensor([pairs[i][1] for i in order], dtype=torch.int32),
                                weight=torch.tensor([pairs[i][2] for i in order], dtype=torch.float32),
-                               expert=[pairs[i][0] for i in order], inverse=inverse)
+                               expert=[pairs[i][0] for i in order], inverse=inverse, real=E if real is None else real)
 
-    def moe_gather_scale(self, x, route):
-        return (x[route.token.long()].float() * route.weight[:, None]).to(x.dtype)
+    def moe_gather_scale(self, x, route, scale=True):
+        rows = x[route.token.long()]
+        return (rows.float() * route.weight[:, None]).to(x.dtype) if scale else rows.clone()
 
-    def moe_expert_gate_up(self, xs, gate, up, route):
+    @staticmethod
+    def _gate_fn(g, u, activation, limit):
+        if activation == "silu":
+            return g / (1 + torch.exp(-g)) * u
+        if activation == "gelu_tanh":
+            return 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))) * u
+        g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+        return g * torch.sigmoid(1.702 * g) * (u + 1)
+
+    def gated_act_mul(self, x, activation, limit=0.0, block=0):
+        i = x.shape[1] // 2
+        return self._gate_fn(x[:, :i].float(), x[:, i:].float(), activation, limit).to(x.dtype)
+
+    def moe_expert_gate_up(self, xs, gate, up, route, gate_up=None, activation="silu", limit=0.0):
         out = torch.zeros(xs.shape[0], gate.shape[1], dtype=xs.dtype)
         for i, e in enumerate(route.expert):
+            if e >= getattr(route, "real", 1 << 30):
+                continue                              # an identity expert has no weights
             g, u2 = gate[e].float() @ xs[i].float(), up[e].float() @ xs[i].float()
-            out[i] = (g / (1 + torch.exp(-g)) * u2).to(xs.dtype)
+            out[i] = self._gate_fn(g, u2, activation, limit).to(xs.dtype)
         return out
 
     def moe_expert_down(self, act, down, route):
         out = torch.zeros(act.shape[0], down.shape[1], dtype=act.dtype)
         for i, e in enumerate(route.expert):
-            out[i] = (down[e].float() @ act[i].float()).to(act.dtype)
+            if e < getattr(route, "real", 1 << 30):
+                out[i] = (down[e].float() @ act[i].float()).to(act.dtype)
+        return out
+
+    def moe_combine_weighted(self, ys, route, x, shared=None, gate_logits=None):
+        T = x.shape[0]
+        rows = ys.float()
+        for i, e in enumerate(route.expert):
+            if e >= route.real:
+                rows[i] = x[int(route.token[i])].float()
+        out = (rows * route.weight[:, None])[route.inverse.long()].reshape(T, route.top, -1).sum(1)
+        if shared is not None:
+            g = torch.sigmoid(gate_logits[:, -1:].float()) if gate_logits is not None else 1.0
+            out = out + g * shared.float()
+        return out.to(ys.dtype)
+
+    # ---- residual streams
+    def stream_step(self, streams, norm_w, eps, out_dtype, read=None, y=None, mix=None, write=None, init_from=None, rows=None):
+        if init_from is not None:
+            streams.copy_(init_from.float()[:, None, :].expand_as(streams))
+        x = streams
+        if y is not None:
+            x = torch.einsum("sr,tsw->trw", mix.float(), streams) + write.float()[None, :, None] * y.float()[:, None, :]
+            if rows is None:
+                streams.copy_(x)
+        if rows is not None:
+            x = x[rows.long()]
+        u = x.sum(1) if read is None else torch.einsum("s,tsw->tw", read.float(), x)
+        return (u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * norm_w.float()).to(out_dtype)
+
+    # ---- attention with a sink
+    def sink_attention_prepare(self, qkv, k_pool, v_pool, inv_freq, rotary_dim, positions, slot_mapping, heads, kv_heads, dim, vdim, eps, page_size):
+        T = qkv.shape[0]
+        Q, K = heads * dim, kv_heads * dim
+
+        def turn(x):           # [T, n, dim] float32
+            if rotary_dim:
+                ang = positions.double()[:, None] * inv_freq[None, :]
+                c, s = torch.cos(ang)[:, None, :].float(), torch.sin(ang)[:, None, :].float()
+                u, v = x[..., 0:rotary_dim:2].clone(), x[..., 1:rotary_dim:2].clone()
+                x[..., 0:rotary_dim:2] = u * c - v * s
+                x[..., 1:rotary_dim:2] = v * c + u * s
+            if eps is not None:
+                x = x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps)
+            return x
+
+        qkv[:, :Q] = turn(qkv[:, :Q].float().reshape(T, heads, dim)).reshape(T, Q).to(qkv.dtype)
+        k = turn(qkv[:, Q : Q + K].float().reshape(T, kv_heads, dim)).to(qkv.dtype)
+        v = qkv[:, Q + K :].reshape(T, kv_heads, vdim)
+        for t in range(T):
+            slot = int(slot_mapping[t])
+            if slot < 0:
+                continue
+            page, off = divmod(slot, page_size)
+            if v_pool is None:
+                k_pool[page, :, off, :dim] = k[t]
+                k_pool[page, :, off, dim:] = v[t]
+            else:
+                k_pool[page, :, off, :] = k[t]
+                v_pool[page, :, off, :] = v[t]
+
+    def sink_attention(self, qkv, k_pool, v_pool, positions, token_row, kv_indptr, kv_indices, heads, kv_heads, dim, vdim, scale, sink, kv_cap=0):
+        T = qkv.shape[0]
+        page_size = k_pool.shape[2]
+        out = torch.zeros(T, heads * vdim, dtype=qkv.dtype)
+        group = heads // kv_heads
+        for t in range(T):
+            pos = int(positions[t])
+            if pos < 0:
+                continue
+            r = int(token_row[t])
+            pages = kv_indices[int(kv_indptr[r]) : int(kv_indptr[r + 1])].long()
+            entries = k_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, k_pool.shape[3])[:, : pos + 1].float()
+            keys = entries[..., :dim]
+            vals = (entries[..., dim:] if v_pool is None
+                    else v_pool[pages].permute(1, 0, 2, 3).reshape(kv_heads, -1, vdim)[:, : pos + 1].float())
+            q = qkv[t, : heads * dim].float().reshape(heads, dim)
+            for h in range(heads):
+                s = (keys[h // group] @ q[h]) * scale
+                m = torch.clamp(s.max(), min=0.0) if sink else s.max()
+                e = torch.exp(s - m)
+                out[t, h * vdim : (h + 1) * vdim] = ((e / (e.sum() + (torch.exp(-m) if sink else 0.0))) @ vals[h // group]).to(qkv.dtype)
+        return out
+
+    # ---- the selective scan
+    def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, N, R):
+        T = xc.shape[0]
+        out = torch.zeros(T, inner, dtype=xc.dtype)
+        for r in range(slots.numel()):
+            lo, hi = int(q_indptr[r]), int(q_indptr[r + 1])
+            S = state[int(slots[r]), : inner * N].reshape(inner, N)
+            for t in range(lo, hi):
+                zdt = dt[t].float() + dt_bias
+                step = torch.where(zdt > 20.0, zdt, torch.log1p(torch.exp(torch.clamp(zdt, max=20.0))))
+                x = xc[t].float()
+                B, C = dbc[t, R : R + N].float(), dbc[t, R + N : R + 2 * N].float()
+                S.copy_(torch.exp(step[:, None] * a) * S + (step * x)[:, None] * B[None, :])
+                y = S @ C + d * x
+                z = xz[t, inner:].float()
+                out[t] = (y * z / (1 + torch.exp(-z))).to(xc.dtype)
         return out
 
     def moe_combine(self, ys, route, shared=None):
