@@ -98,6 +98,21 @@ __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The gate functions of gated feed-forwards, on the 32-bit gate and up values: silu(g) u; the tanh form of GELU times u; the
+// clamped swish, with g = min(g, limit) and u = clamp(u, -limit, limit): g sigmoid(1.702 g) (u + 1).
+__device__ __forceinline__ float gate_fn(float g, float u, int act, float limit) {
+  if (act == ROOST_ACT_GELU_TANH) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(z)) * u;
+  }
+  if (act == ROOST_ACT_CLAMPED_SWISH) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
 // Weight vectors (norm weights) may be stored in either dtype whatever the activations are.
 __device__ __forceinline__ float load_w(const void* w, int i, int wdtype) {
   return wdtype == ROOST_F32 ? reinterpret_cast<const float*>(w)[i]

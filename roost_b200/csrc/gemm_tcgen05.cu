@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(192, 1)
 template <typename TOut, int EPI>
 __global__ void __launch_bounds__(192, 1)
     gemm_tcgen05_grouped_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, TOut* __restrict__ out,
-                                const int32_t* __restrict__ tile_list, int m_tiles, int N, int K, int64_t ldo) {
+                                const int32_t* __restrict__ tile_list, int m_tiles, int N, int K, int64_t ldo, int act, float limit) {
   extern __shared__ unsigned char smem_raw[];
   // tiles want 1024-byte alignment (the swizzle pattern repeats every 1024 bytes)
   const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(192, 1)
           tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), g);
           tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + BN / 2 + c * 32), u);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]));
+          for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(gate_fn(__uint_as_float(g[i]), __uint_as_float(u[i]), act, limit));
           const int col = n0 / 2 + c * 32;
           if (row < M && col < n_out) store_row32<TOut>(out + (size_t)row * ldo + col, g, n_out - col, vec_ok);
         }
@@ -1286,7 +1286,7 @@ extern "C" int roost_gemm_tcgen05_status(void) {
 
 template <int EPI>
 static int launch_tcgen05_grouped(const CUtensorMap& ma, const CUtensorMap& mb, void* out, const int32_t* tile_list, int m_tiles, int n, int k,
-                                  int64_t ldo, cudaStream_t s) {
+                                  int64_t ldo, int act, float limit, cudaStream_t s) {
   static int sms = 0;
   static bool attr_set = false;
   const size_t smem = (size_t)STAGES * kStageBytes + 1024;
@@ -1300,16 +1300,16 @@ static int launch_tcgen05_grouped(const CUtensorMap& ma, const CUtensorMap& mb, 
   }
   const long long tiles = (long long)m_tiles * ((n + BN - 1) / BN);
   const int grid = tiles < sms ? (int)tiles : sms;
-  kernel<<<grid, 192, smem, s>>>(ma, mb, (__nv_bfloat16*)out, tile_list, m_tiles, n, k, ldo);
+  kernel<<<grid, 192, smem, s>>>(ma, mb, (__nv_bfloat16*)out, tile_list, m_tiles, n, k, ldo, act, limit);
   return check_launch("gemm_tcgen05_grouped");
 }
 
 // Rows of a sorted by expert against the experts' matrices w [experts, n, k] (contiguous): out[row, :] = a[row, :] w[e]^T, or
-// with swiglu (n = 2 * inter, an expert's rows interleaved in blocks of 128 gate rows then their 128 up rows)
-// out[row, :] = silu(gate) * up of n / 2 columns. tile_list: m_tiles triples (expert, first row, one past the last row) of at
+// with gated != 0 (n = 2 * inter, an expert's rows interleaved in blocks of 128 gate rows then their 128 up rows)
+// out[row, :] = act(gate, up) of n / 2 columns (the gate functions of common.cuh). tile_list: m_tiles triples (expert, first row, one past the last row) of at
 // most 128 rows each, expert -1 for unused entries.
 extern "C" int roost_gemm_tcgen05_grouped(const void* a, const void* w, void* out, const int32_t* tile_list, int m_tiles, int rows,
-                                          int experts, int n, int k, int swiglu, roost_stream_t stream) {
+                                          int experts, int n, int k, int swiglu, int act, float limit, roost_stream_t stream) {
   ROOST_REQUIRE(rows > 0 && experts > 0 && n > 0 && k > 0 && m_tiles > 0 && tile_list != nullptr, "gemm_tcgen05_grouped: sizes must be positive");
   if (k % 8 != 0 || (swiglu && n % 256 != 0) || (long long)experts * n > 2147483647LL) {
     return fail(ROOST_ERR_UNSUPPORTED, "gemm_tcgen05_grouped: k must be a multiple of 8 and, with swiglu, n a multiple of 256");
@@ -1320,8 +1320,9 @@ extern "C" int roost_gemm_tcgen05_grouped(const void* a, const void* w, void* ou
   if (rc != ROOST_OK) return rc;
   rc = make_map(&mb, w, experts * n, k, k, BN);
   if (rc != ROOST_OK) return rc;
-  if (swiglu) return launch_tcgen05_grouped<1>(ma, mb, out, tile_list, m_tiles, n, k, n / 2, (cudaStream_t)stream);
-  return launch_tcgen05_grouped<0>(ma, mb, out, tile_list, m_tiles, n, k, n, (cudaStream_t)stream);
+  ROOST_REQUIRE(act >= ROOST_ACT_SILU && act <= ROOST_ACT_CLAMPED_SWISH, "gemm_tcgen05_grouped: unknown gate function");
+  if (swiglu) return launch_tcgen05_grouped<1>(ma, mb, out, tile_list, m_tiles, n, k, n / 2, act, limit, (cudaStream_t)stream);
+  return launch_tcgen05_grouped<0>(ma, mb, out, tile_list, m_tiles, n, k, n, act, limit, (cudaStream_t)stream);
 }
 
 extern "C" int roost_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw, int64_t ldo,

@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 12
+#define ROOST_ABI_VERSION 13
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -26,6 +26,12 @@ extern "C" {
 
 #define ROOST_F32 0
 #define ROOST_BF16 1
+
+/* gate functions of gated feed-forwards, applied to the 32-bit gate g and up u: silu(g) u; gelu_tanh(g) u; with g = min(g,
+ * limit) and u = clamp(u, -limit, limit): g sigmoid(1.702 g) (u + 1) */
+#define ROOST_ACT_SILU 0
+#define ROOST_ACT_GELU_TANH 1
+#define ROOST_ACT_CLAMPED_SWISH 2
 
 typedef void* roost_stream_t;
 
@@ -305,27 +311,70 @@ int roost_gated_group_norm(const float* y, const void* u, int64_t ld_u, const fl
 int roost_moe_tile_rows(void);   /* rows of a tile of sorted rows */
 /* out[t, e] = x[t, :] . w[e, :] in 32-bit. */
 int roost_moe_router_logits(const void* x, const void* w, float* out, int tokens, int hidden, int experts, int dtype, roost_stream_t stream);
-/* scratch: int32[2 * tokens * top]; tiles: int32[3 * max_tiles], max_tiles >= ceil(tokens * top / tile rows) + experts;
- * counts: int32[experts], zero on entry and left at zero. */
+/* scratch: int32[3 * tokens * top]; tiles: int32[3 * max_tiles], max_tiles >= ceil(tokens * top / tile rows) + experts;
+ * counts: int32[experts], zero on entry and left at zero. mode 0: sigmoid scores, compared by logit. mode 1: softmax scores
+ * over the `experts` routed columns of a row of `columns` logits, compared with correction[e] (may be null) added; a pair's
+ * weight is score * scale. Experts from `real` on (identity experts) get sorted rows but no tiles. */
 /* wide_tiles (may be null): the same rows cut into tiles of roost_moe_wide_tile_rows() rows, int32[3 * max_wide_tiles], for
  * roost_gemm_tcgen05_grouped. */
 int roost_moe_wide_tile_rows(void);
-int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
-                    int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* wide_tiles, int max_wide_tiles,
-                    int32_t* scratch, int32_t* counts, roost_stream_t stream);
+int roost_moe_route(const float* logits, int tokens, int columns, int experts, int real, int top, int mode, const float* correction,
+                    float scale, int32_t* token_of, float* weight_of, int32_t* expert_of, int32_t* inverse, int32_t* offsets, int32_t* tiles,
+                    int max_tiles, int32_t* wide_tiles, int max_wide_tiles, int32_t* scratch, int32_t* counts, roost_stream_t stream);
 /* Sorted rows against the experts' matrices w [experts, n, k] on tcgen05 (gemm_tcgen05.cu): out[row, :] = a[row, :] w[e]^T, or
- * with swiglu (n = 2 * inter, an expert's rows in blocks of 128 gate rows then their 128 up rows) silu(gate) * up of n / 2
- * columns. tile_list: the route's wide tiles. k a multiple of 8; with swiglu n a multiple of 256. */
+ * with gated != 0 (n = 2 * inter, an expert's rows in blocks of 128 gate rows then their 128 up rows) the gate function `act`
+ * of gate and up, n / 2 columns. tile_list: the route's wide tiles. k a multiple of 8; gated: n a multiple of 256. */
 int roost_gemm_tcgen05_grouped(const void* a, const void* w, void* out, const int32_t* tile_list, int m_tiles, int rows, int experts,
-                               int n, int k, int swiglu, roost_stream_t stream);
-int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
-                           roost_stream_t stream);
-/* out[row, :] = a[row, :] w1[e]^T (w2 null) or silu(a w1[e]^T) * (a w2[e]^T), e the row's expert; w: [experts, n, k]. With
+                               int n, int k, int gated, int act, float limit, roost_stream_t stream);
+/* xs[row, :] = x[token_of[row], :], times weight_of[row] (rounded once) when scaled != 0. */
+int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int scaled,
+                           int dtype, roost_stream_t stream);
+/* out[row, :] = a[row, :] w1[e]^T (w2 null) or act(a w1[e]^T, a w2[e]^T), e the row's expert; w: [experts, n, k]. With
  * block > 0 the gated form's weights are one tensor, w1 = [experts, 2 n, k], an expert's rows interleaved in blocks of
- * `block` gate rows then their `block` up rows (w2: any non-null value). */
+ * `block` gate rows then their `block` up rows (w2: any non-null value). Rows of experts from `real` on are skipped (form 1;
+ * form 0 has no tiles for them). */
 int roost_moe_expert_gemm(const void* a, const void* w1, const void* w2, void* out, const int32_t* tiles, int max_tiles,
-                          const int32_t* expert_of, int rows, int n, int k, int form, int block, int dtype, roost_stream_t stream);
+                          const int32_t* expert_of, int rows, int n, int k, int form, int block, int act, float limit, int real, int dtype,
+                          roost_stream_t stream);
 int roost_moe_combine(const void* ys, const int32_t* inverse, const void* shared, void* out, int tokens, int hidden, int top, int dtype,
+                      roost_stream_t stream);
+/* out[t, :] = sum_k weight_of[r] * (expert_of[r] < real ? ys[r, :] : x[t, :]), r = inverse[t * top + k], plus, with shared,
+ * sigmoid(gate[t * gate_stride]) * shared[t, :] (gate null: plus shared). */
+int roost_moe_combine_weighted(const void* ys, const int32_t* inverse, const float* weight_of, const int32_t* expert_of, const void* x,
+                               const void* shared, const float* gate, int gate_stride, void* out, int tokens, int hidden, int top, int real,
+                               int dtype, roost_stream_t stream);
+
+/* ---- several 32-bit residual streams a token; gate functions (residual_streams.cu) ---- */
+/* streams: float[tokens, n_streams, width]. Per output row i (token t = rows ? rows[i] : i): with init_from every stream
+ * becomes a copy of init_from[t, :]; with y (and mix [from, to], write) x'_r = sum_s mix[s, r] x_s + write[r] y[t, :], stored unless
+ * rows is given; then u = sum_s read[s] x'_s (read null: the plain sum) and out[i, :] = u / sqrt(mean(u^2) + eps) * norm_w. */
+int roost_stream_step(float* streams, const void* y, const void* init_from, const float* mix, const float* write, const float* read,
+                      const float* norm_w, const int32_t* rows, void* out, int n_out, int n_streams, int width, float eps, int dtype,
+                      roost_stream_t stream);
+/* out[t, i] = act(gate[t, i], up[t, i]) over rows [gate | up] (block 0) or blocks of `block` gate then `block` up values. */
+int roost_gated_act_mul(const void* x, void* out, int tokens, int inter, int block, int act, float limit, int dtype, roost_stream_t stream);
+
+/* ---- attention with a sink, unit-norm heads and values of their own size (sink_attention.cu) ---- */
+/* qkv rows [q heads | k heads | v heads] with row stride ld: rotation of interleaved pairs and unit root mean square (eps <= 0:
+ * none) on q (in place) and k; k and v to the cache entry of the token's slot: ((page * kv_heads + head) * page_size + offset) *
+ * entry from k_base and v_base. */
+int roost_sink_attention_prepare(void* qkv, int64_t ld, void* k_base, void* v_base, int entry, const double* inv_freq,
+                                 const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                 int rot_dims, float eps, int page_size, int dtype, roost_stream_t stream);
+/* out [tokens, heads * vdim]. sink != 0: one is added to the softmax's denominator. splits > 1: a token's key tiles of 32 are
+ * dealt in ranges of tiles_per_split to `splits` blocks whose partials (part: float[tokens * heads * splits * (vdim + 2)]) a
+ * second kernel combines. */
+int roost_sink_attention(const void* qkv, int64_t ld, void* out, float* part, const void* k_base, const void* v_base, int entry,
+                         const int32_t* positions, const int32_t* token_row, const int32_t* kv_indptr, const int32_t* kv_indices, int tokens,
+                         int heads, int kv_heads, int dim, int vdim, int page_size, float scale, int sink, int splits, int tiles_per_split,
+                         int dtype, roost_stream_t stream);
+
+/* ---- the Mamba selective scan (mamba1.cu) ---- */
+/* Per (row, channel): dt = softplus(dt_raw + dt_bias); S <- exp(dt a_neg) S + dt x B; y = S . C + d_skip x; out = y silu(z). xc
+ * [tokens, inner]; dt_raw float[tokens, inner]; dbc rows [dt | B | C]; xz rows [x | z]; state slots [inner * n_state | ...]. */
+int roost_mamba1_scan(const void* xc, const float* dt_raw, const void* dbc, int64_t ld_dbc, const void* xz, int64_t ld_xz, void* out,
+                      const float* dt_bias, const float* a_neg, const float* d_skip, float* state, int64_t state_stride,
+                      const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int inner, int n_state, int dt_rank, int dtype,
                       roost_stream_t stream);
 
 #ifdef __cplusplus

@@ -11,6 +11,14 @@
 //                 rows on FFMA (every output sums over k in increasing order in one thread), and, for the few rows of a decode
 //                 step, a warp an output that streams the row's expert with 16-byte loads.
 //   combine:      out[t, :] = sum_k ys[inverse[t * top + k], :] (+ shared[t, :]), summed in 32-bit in the order of k.
+//
+// A second form of routing (mode 1): scores are the softmax of the first `experts` logits of a token's row of `columns` logits
+// (a row may carry further columns that are not routed); the choice compares score + correction[e], the weight of a pair is
+// score * scale; experts from `real` on are identity experts: they get sorted rows like the others but no tiles, the expert
+// products skip their rows, and combine_weighted takes the token's own row for them:
+//   combine_weighted: out[t, :] = sum_k weight[r_k] * (expert[r_k] < real ? ys[r_k, :] : x[t, :]) (+ sigmoid(gate[t]) * shared[t, :]),
+//                 r_k = inverse[t * top + k], summed in 32-bit in the order of k.
+// The gated expert product applies the gate function of common.cuh (silu, the tanh form of GELU, the clamped swish).
 #include "common.cuh"
 
 #include <mma.h>
@@ -53,19 +61,39 @@ __global__ void __launch_bounds__(256) moe_router_logits_kernel(const T* __restr
 // A warp a token: the token's logits in shared memory, `top` rounds of a warp-wide argmax (ties to the lower index); the
 // choice's place among its expert's rows is the expert's running count (the order within an expert is that of arrival:
 // every row is computed for itself, so the order changes no value).
-__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int tokens, int experts, int top,
+__global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__ logits, int tokens, int columns, int experts, int top,
+                                                      int mode, const float* __restrict__ correction, float scale,
                                                       int32_t* __restrict__ pair_expert, int32_t* __restrict__ pair_rank,
-                                                      int32_t* __restrict__ counts) {
-  extern __shared__ float zs[];          // [8 warps][experts]
+                                                      float* __restrict__ pair_weight, int32_t* __restrict__ counts) {
+  extern __shared__ float zs[];          // [8 warps][experts] what is compared, then [8 warps][experts] the scores (mode 1)
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 8 + warp;
   pdl_wait();
   if (t >= tokens) return;
   float* z = zs + (size_t)warp * experts;
+  float* sc = zs + (size_t)(8 + warp) * experts;
+  float zmax = -3.0e38f;
   for (int e = lane; e < experts; e += 32) {
-    const float v = logits[(size_t)t * experts + e];
+    const float v = logits[(size_t)t * columns + e];
     z[e] = v == v ? fmaxf(v, -3.0e38f) : -3.0e38f;     // a NaN or -inf is the smallest score, not a hole in the order
+    zmax = fmaxf(zmax, z[e]);
+  }
+  if (mode == 1) {       // softmax scores over all routed columns; the choice sees score + correction
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) {
+      const float ev = expf(z[e] - zmax);
+      sc[e] = ev;
+      sum += ev;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < experts; e += 32) {
+      const float score = sc[e] * inv;
+      sc[e] = score * scale;
+      z[e] = score + (correction != nullptr ? correction[e] : 0.f);
+    }
   }
   __syncwarp();
   for (int k = 0; k < top; ++k) {
@@ -91,6 +119,7 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__
       z[best] = -INFINITY;               // taken
       pair_expert[(size_t)t * top + k] = best;
       pair_rank[(size_t)t * top + k] = atomicAdd(&counts[best], 1);
+      if (mode == 1) pair_weight[(size_t)t * top + k] = sc[best];
     }
     __syncwarp();
   }
@@ -98,7 +127,8 @@ __global__ void __launch_bounds__(256) moe_topk_kernel(const float* __restrict__
 
 // One block: the experts' counts become their row ranges and the list of tiles, every pair goes to its sorted row, and the
 // counts are left at zero for the next call.
-__global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict__ logits, int tokens, int experts, int top,
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict__ logits, int tokens, int columns, int experts, int real, int top,
+                                                       int mode, const float* __restrict__ pair_weight,
                                                        int32_t* __restrict__ token_of, float* __restrict__ weight_of,
                                                        int32_t* __restrict__ expert_of, int32_t* __restrict__ inverse,
                                                        int32_t* __restrict__ offsets, int32_t* __restrict__ tiles, int max_tiles,
@@ -114,7 +144,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
       const int c = counts[e];
       offs[e] = at;
       offsets[e] = at;
-      for (int r = at; r < at + c; r += kMoeTile) {
+      for (int r = at; r < at + c && e < real; r += kMoeTile) {
         tiles[3 * n] = e;
         tiles[3 * n + 1] = r;
         tiles[3 * n + 2] = min(r + kMoeTile, at + c);
@@ -130,7 +160,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
     int at = 0, n = 0;
     for (int e = 0; e < experts; ++e) {
       const int c = counts[e];
-      for (int r = at; r < at + c; r += kMoeWideTile) {
+      for (int r = at; r < at + c && e < real; r += kMoeWideTile) {
         wide_tiles[3 * n] = e;
         wide_tiles[3 * n + 1] = r;
         wide_tiles[3 * n + 2] = min(r + kMoeWideTile, at + c);
@@ -145,9 +175,9 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
   for (int i = threadIdx.x; i < tokens * top; i += blockDim.x) {
     const int e = pair_expert[i];
     const int dest = offs[e] + pair_rank[i];
-    const float z = logits[(size_t)(i / top) * experts + e];
+    const float z = logits[(size_t)(i / top) * columns + e];
     token_of[dest] = i / top;
-    weight_of[dest] = 1.0f / (1.0f + expf(-z));
+    weight_of[dest] = mode == 1 ? pair_weight[i] : 1.0f / (1.0f + expf(-z));
     expert_of[dest] = e;
     inverse[i] = dest;
   }
@@ -155,12 +185,16 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const float* __restrict_
 
 template <typename T>
 __global__ void moe_gather_scale_kernel(const T* __restrict__ x, T* __restrict__ xs, const int32_t* __restrict__ token_of,
-                                        const float* __restrict__ weight_of, int hidden) {
+                                        const float* __restrict__ weight_of, int hidden, int scaled) {
   pdl_launch_dependents();
   pdl_wait();
   const int row = blockIdx.x;
   const T* src = x + (size_t)token_of[row] * hidden;
   const float w = weight_of[row];
+  if (!scaled) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[(size_t)row * hidden + i] = src[i];
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[(size_t)row * hidden + i] = from_float<T>(w * to_float(src[i]));
 }
 
@@ -179,7 +213,8 @@ __device__ __forceinline__ size_t moe_weight_row(int n, int block) {
 // is silu(a Wg^T) * (a Wu^T).
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
-                                                           T* __restrict__ out, const int32_t* __restrict__ tiles, int N, int K, int block) {
+                                                           T* __restrict__ out, const int32_t* __restrict__ tiles, int N, int K, int block, int act,
+                                                           float limit) {
   constexpr int BM = kMoeTile, BN = 64, BK = 16;
   __shared__ float as[BK][BM + 1];
   __shared__ float ws1[BK][BN + 1];
@@ -242,9 +277,7 @@ __global__ void __launch_bounds__(256) moe_tile_gemm_kernel(const T* __restrict_
       const int n = n0 + tx * 4 + j;
       if (n >= N) continue;
       float v = acc1[i][j];
-      if (GATED) {
-        v = v / (1.0f + expf(-v)) * acc2[i][j];     // on the 32-bit sums
-      }
+      if (GATED) v = gate_fn(v, acc2[i][j], act, limit);     // on the 32-bit sums
       out[(size_t)m * N + n] = from_float<T>(v);
     }
   }
@@ -266,7 +299,7 @@ constexpr int moe_tc_stage_elems(bool gated) { return (kMoeTile + (gated ? 2 : 1
 template <bool GATED>
 __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w1,
                                                               const __nv_bfloat16* __restrict__ w2, __nv_bfloat16* __restrict__ out,
-                                                              const int32_t* __restrict__ tiles, int N, int K, int block) {
+                                                              const int32_t* __restrict__ tiles, int N, int K, int block, int act, float limit) {
   using namespace nvcuda;
   constexpr int BM = kMoeTile, BN = kMoeTcBN, BK = kMoeTcBK, LD = kMoeTcLD, STAGE = moe_tc_stage_elems(GATED);
   extern __shared__ __align__(128) unsigned char raw[];
@@ -358,9 +391,7 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           v[c] = patch[pr * 20 + pc + c];
-          if (GATED) {
-            v[c] = v[c] / (1.0f + expf(-v[c])) * patch[16 * 20 + pr * 20 + pc + c];     // on the 32-bit sums
-          }
+          if (GATED) v[c] = gate_fn(v[c], patch[16 * 20 + pr * 20 + pc + c], act, limit);     // on the 32-bit sums
         }
         __nv_bfloat16* dst = out + (size_t)m * N + n;
         if (n + 8 <= N && N % 8 == 0) {
@@ -376,7 +407,8 @@ __global__ void __launch_bounds__(128) moe_tile_gemm_tc_kernel(const __nv_bfloat
 // Few rows: a block per sorted row and 8 outputs, a warp an output; lanes stride over k.
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w1, const T* __restrict__ w2,
-                                                          T* __restrict__ out, const int32_t* __restrict__ expert_of, int N, int K, int block) {
+                                                          T* __restrict__ out, const int32_t* __restrict__ expert_of, int N, int K, int block, int act,
+                                                          float limit, int real) {
   constexpr int V = Vec<T>::N;
   pdl_launch_dependents();
   const int row = blockIdx.x;
@@ -385,6 +417,7 @@ __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__
   pdl_wait();
   if (n >= N) return;
   const int e = expert_of[row];
+  if (e >= real) return;              // an identity expert has no weights; nobody reads its row of the output
   const T* ar = a + (size_t)row * K;
   const T* wr1 = moe_expert_base(w1, e, N, K, block) + moe_weight_row(n, block) * K;
   const T* wr2 = GATED ? (block ? wr1 + (size_t)block * K : w2 + ((size_t)e * N + n) * K) : nullptr;
@@ -413,9 +446,7 @@ __global__ void __launch_bounds__(256) moe_row_gemm_kernel(const T* __restrict__
   if (GATED) s2 = warp_sum(s2);
   if (lane == 0) {
     float v = s1;
-    if (GATED) {
-      v = s1 / (1.0f + expf(-s1)) * s2;     // on the 32-bit sums
-    }
+    if (GATED) v = gate_fn(s1, s2, act, limit);     // on the 32-bit sums
     out[(size_t)row * N + n] = from_float<T>(v);
   }
 }
@@ -430,6 +461,33 @@ __global__ void moe_combine_kernel(const T* __restrict__ ys, const int32_t* __re
     float acc = 0.f;
     for (int k = 0; k < top; ++k) acc += to_float(ys[(size_t)inverse[(size_t)t * top + k] * hidden + i]);
     if (shared) acc += to_float(shared[(size_t)t * hidden + i]);
+    out[(size_t)t * hidden + i] = from_float<T>(acc);
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_weighted_kernel(const T* __restrict__ ys, const int32_t* __restrict__ inverse, const float* __restrict__ weight_of,
+                                            const int32_t* __restrict__ expert_of, const T* __restrict__ x, const T* __restrict__ shared,
+                                            const float* __restrict__ gate, int gate_stride, T* __restrict__ out, int hidden, int top, int real) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  __shared__ int32_t rk[kMoeMaxTop];
+  __shared__ float wk[kMoeMaxTop];
+  __shared__ int idk[kMoeMaxTop];
+  if (threadIdx.x < top) {
+    const int r = inverse[(size_t)t * top + threadIdx.x];
+    rk[threadIdx.x] = r;
+    wk[threadIdx.x] = weight_of[r];
+    idk[threadIdx.x] = expert_of[r] >= real;
+  }
+  __syncthreads();
+  const float g = (shared != nullptr && gate != nullptr) ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride])) : 1.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float acc = 0.f;
+    const float xv = to_float(x[(size_t)t * hidden + i]);
+    for (int k = 0; k < top; ++k) acc = fmaf(wk[k], idk[k] ? xv : to_float(ys[(size_t)rk[k] * hidden + i]), acc);
+    if (shared) acc = fmaf(g, to_float(shared[(size_t)t * hidden + i]), acc);
     out[(size_t)t * hidden + i] = from_float<T>(acc);
   }
 }
@@ -454,10 +512,16 @@ extern "C" int roost_moe_router_logits(const void* x, const void* w, float* out,
 // counts: int32[experts], zero on entry and left at zero (a caller keeps one buffer for all its calls on a stream).
 extern "C" int roost_moe_wide_tile_rows(void) { return kMoeWideTile; }
 
-extern "C" int roost_moe_route(const float* logits, int tokens, int experts, int top, int32_t* token_of, float* weight_of, int32_t* expert_of,
-                               int32_t* inverse, int32_t* offsets, int32_t* tiles, int max_tiles, int32_t* wide_tiles, int max_wide_tiles,
-                               int32_t* scratch, int32_t* counts, roost_stream_t stream) {
-  ROOST_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts, "moe_route: sizes do not fit");
+// mode 0: sigmoid scores, compared by logit; mode 1: softmax scores over the `experts` routed columns of a row of `columns`,
+// compared with `correction` (may be null) added, weights times `scale`. Experts from `real` on have no tiles. scratch: 3 * tokens *
+// top 32-bit words.
+extern "C" int roost_moe_route(const float* logits, int tokens, int columns, int experts, int real, int top, int mode, const float* correction,
+                               float scale, int32_t* token_of, float* weight_of, int32_t* expert_of, int32_t* inverse, int32_t* offsets,
+                               int32_t* tiles, int max_tiles, int32_t* wide_tiles, int max_wide_tiles, int32_t* scratch, int32_t* counts,
+                               roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && experts > 0 && top > 0 && top <= experts && columns >= experts && real >= 0 && real <= experts,
+                "moe_route: sizes do not fit");
+  ROOST_REQUIRE(mode == 0 || mode == 1, "moe_route: the mode is 0 (sigmoid) or 1 (softmax)");
   if (top > kMoeMaxTop || experts > 4096) return fail(ROOST_ERR_UNSUPPORTED, "moe_route: more than 32 choices a token or 4096 experts");
   ROOST_REQUIRE((int64_t)max_tiles >= ((int64_t)tokens * top + kMoeTile - 1) / kMoeTile + experts, "moe_route: the tile list is too short");
   ROOST_REQUIRE(counts != nullptr && scratch != nullptr, "moe_route: a pointer is null");
@@ -466,20 +530,21 @@ extern "C" int roost_moe_route(const float* logits, int tokens, int experts, int
   if (tokens == 0) return ROOST_OK;
   int32_t* pair_expert = scratch;
   int32_t* pair_rank = scratch + (size_t)tokens * top;
-  launch_kernel(moe_topk_kernel, dim3((tokens + 7) / 8), dim3(256), (size_t)8 * experts * sizeof(float), (cudaStream_t)stream, logits, tokens,
-                experts, top, pair_expert, pair_rank, counts);
-  launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), ((size_t)experts + 1) * sizeof(int32_t), (cudaStream_t)stream, logits, tokens, experts, top,
-                token_of, weight_of, expert_of, inverse, offsets, tiles, max_tiles, wide_tiles, max_wide_tiles, (const int32_t*)pair_expert,
+  float* pair_weight = reinterpret_cast<float*>(scratch + (size_t)2 * tokens * top);
+  launch_kernel(moe_topk_kernel, dim3((tokens + 7) / 8), dim3(256), (size_t)16 * experts * sizeof(float), (cudaStream_t)stream, logits, tokens,
+                columns, experts, top, mode, correction, scale, pair_expert, pair_rank, pair_weight, counts);
+  launch_kernel(moe_sort_kernel, dim3(1), dim3(1024), ((size_t)experts + 1) * sizeof(int32_t), (cudaStream_t)stream, logits, tokens, columns, experts,
+                real, top, mode, (const float*)pair_weight, token_of, weight_of, expert_of, inverse, offsets, tiles, max_tiles, wide_tiles, max_wide_tiles, (const int32_t*)pair_expert,
                 (const int32_t*)pair_rank, counts);
   return check_launch("moe_route");
 }
 
-extern "C" int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int dtype,
-                                      roost_stream_t stream) {
+extern "C" int roost_moe_gather_scale(const void* x, void* xs, const int32_t* token_of, const float* weight_of, int rows, int hidden, int scaled,
+                                      int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && hidden > 0, "moe_gather_scale: sizes must be positive");
   if (rows == 0) return ROOST_OK;
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(moe_gather_scale_kernel<T>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const T*)x, (T*)xs,
-                                               token_of, weight_of, hidden));
+                                               token_of, weight_of, hidden, scaled));
   return check_launch("moe_gather_scale");
 }
 
@@ -487,8 +552,11 @@ extern "C" int roost_moe_gather_scale(const void* x, void* xs, const int32_t* to
 // block > 0: the gated product's weights are one tensor, w1 = [experts, 2 n, k] with gate and up rows interleaved in blocks of
 // `block` (w2 is then only a flag: any non-null value).
 extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* w2, void* out, const int32_t* tiles, int max_tiles,
-                                     const int32_t* expert_of, int rows, int n, int k, int form, int block, int dtype, roost_stream_t stream) {
+                                     const int32_t* expert_of, int rows, int n, int k, int form, int block, int act, float limit, int real,
+                                     int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && n > 0 && k > 0 && (form == 0 || form == 1), "moe_expert_gemm: sizes do not fit");
+  ROOST_REQUIRE(act >= ROOST_ACT_SILU && act <= ROOST_ACT_CLAMPED_SWISH && (act != ROOST_ACT_CLAMPED_SWISH || limit > 0.f || w2 == nullptr),
+                "moe_expert_gemm: unknown gate function, or a clamped swish without its limit");
   ROOST_REQUIRE(block >= 0 && (block == 0 || (w2 != nullptr && n % block == 0)), "moe_expert_gemm: an interleave block must divide n and belongs to the gated form");
   if (block) w2 = w1;
   if (rows == 0) return ROOST_OK;
@@ -503,23 +571,23 @@ extern "C" int roost_moe_expert_gemm(const void* a, const void* w1, const void* 
       const size_t smem = (size_t)kMoeTcStages * moe_tc_stage_elems(w2 != nullptr) * sizeof(B);
       if (w2) {
         cudaFuncSetAttribute(moe_tile_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_kernel(moe_tile_gemm_tc_kernel<true>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k, block);
+        launch_kernel(moe_tile_gemm_tc_kernel<true>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k, block, act, limit);
       } else {
         cudaFuncSetAttribute(moe_tile_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_kernel(moe_tile_gemm_tc_kernel<false>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k, block);
+        launch_kernel(moe_tile_gemm_tc_kernel<false>, tc_grid, dim3(128), smem, s, (const B*)a, (const B*)w1, (const B*)w2, (B*)out, tiles, n, k, block, act, limit);
       }
       return check_launch("moe_expert_gemm");
     }
     ROOST_DISPATCH_DTYPE(dtype, T, {
-      if (w2) launch_kernel(moe_tile_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k, block);
-      else launch_kernel(moe_tile_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k, block);
+      if (w2) launch_kernel(moe_tile_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k, block, act, limit);
+      else launch_kernel(moe_tile_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, tiles, n, k, block, act, limit);
     });
   } else {
     dim3 grid(rows, (n + 7) / 8);
     if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "moe_expert_gemm: too many outputs");
     ROOST_DISPATCH_DTYPE(dtype, T, {
-      if (w2) launch_kernel(moe_row_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k, block);
-      else launch_kernel(moe_row_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k, block);
+      if (w2) launch_kernel(moe_row_gemm_kernel<T, true>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k, block, act, limit, real);
+      else launch_kernel(moe_row_gemm_kernel<T, false>, grid, dim3(256), 0, s, (const T*)a, (const T*)w1, (const T*)w2, (T*)out, expert_of, n, k, block, act, limit, real);
     });
   }
   return check_launch("moe_expert_gemm");
@@ -532,4 +600,15 @@ extern "C" int roost_moe_combine(const void* ys, const int32_t* inverse, const v
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(moe_combine_kernel<T>, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, (const T*)ys, inverse,
                                                (const T*)shared, (T*)out, hidden, top));
   return check_launch("moe_combine");
+}
+
+extern "C" int roost_moe_combine_weighted(const void* ys, const int32_t* inverse, const float* weight_of, const int32_t* expert_of, const void* x,
+                                          const void* shared, const float* gate, int gate_stride, void* out, int tokens, int hidden, int top,
+                                          int real, int dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && hidden > 0 && top > 0 && top <= kMoeMaxTop, "moe_combine_weighted: sizes do not fit");
+  ROOST_REQUIRE(ys && inverse && weight_of && expert_of && x && out, "moe_combine_weighted: a pointer is null");
+  if (tokens == 0) return ROOST_OK;
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(moe_combine_weighted_kernel<T>, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, (const T*)ys, inverse,
+                                               weight_of, expert_of, (const T*)x, (const T*)shared, gate, gate_stride, (T*)out, hidden, top, real));
+  return check_launch("moe_combine_weighted");
 }

@@ -14,8 +14,9 @@ import torch
 
 from . import build
 
-ABI_VERSION = 12
+ABI_VERSION = 13
 F32, BF16 = 0, 1
+GATE_FUNCTIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}   # the codes of csrc/roost_kernels.h
 
 
 class KernelError(RuntimeError):
@@ -125,11 +126,23 @@ _SIGNATURES = {
     "roost_moe_tile_rows": [],
     "roost_moe_router_logits": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_wide_tile_rows": [],
-    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                        c_void_p, c_void_p, c_void_p],
-    "roost_gemm_tcgen05_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
-    "roost_moe_gather_scale": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_moe_route": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
+    "roost_gemm_tcgen05_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "roost_moe_gather_scale": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_moe_expert_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                              c_int, c_int, c_void_p],
+    "roost_moe_combine_weighted": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                   c_int, c_int, c_void_p],
+    "roost_stream_step": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                          c_int, c_void_p],
+    "roost_gated_act_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_sink_attention_prepare": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_float, c_int, c_int, c_void_p],
+    "roost_sink_attention": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_mamba1_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "roost_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_argmax_split": [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -154,6 +167,7 @@ class MoeRoute:
     tiles: torch.Tensor
     max_tiles: int
     form: int
+    real: int = 1 << 30                        # experts from here on are identity experts: rows without weights
     wide_tiles: torch.Tensor | None = None     # the same rows in tiles of 128, for the tcgen05 product of steps of many rows
     max_wide_tiles: int = 0
 
@@ -382,7 +396,9 @@ class KernelLibrary:
 
     def gemm_simt(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         """a [M, K] times w [N, K] transposed, 32-bit FFMA accumulation."""
-        _need(a, "a"); _need(w, "w", a.dtype)
+        _need(w, "w", a.dtype)
+        if not a.is_cuda or a.dim() != 2 or (a.shape[1] > 1 and a.stride(1) != 1):       # rows may be strided (a column range of wider rows)
+            raise KernelError("a is not a CUDA matrix with dense rows")
         M, K = a.shape
         N, K2 = w.shape
         if K != K2:
@@ -649,9 +665,21 @@ class KernelLibrary:
         self._call("roost_moe_router_logits", _ptr(x), _ptr(w), _ptr(out), T, H, E, dtype_code(x.dtype), _stream())
         return out
 
-    def moe_route(self, logits: torch.Tensor, top: int) -> MoeRoute:
+    def moe_route(self, logits: torch.Tensor, top: int, score: str = "sigmoid", correction: torch.Tensor | None = None, scale: float = 1.0,
+                  routed: int | None = None, real: int | None = None) -> MoeRoute:
+        """``score`` "sigmoid": the weights are the sigmoid of the chosen logits. "softmax": scores are the softmax over the first
+        ``routed`` columns (default all), ``correction`` is added for the choice only, the weights are score * ``scale``; experts
+        from ``real`` on are identity experts (sorted rows, no tiles)."""
         _need(logits, "logits", torch.float32)
-        T, E = logits.shape
+        T, columns = logits.shape
+        E = columns if routed is None else routed
+        real = E if real is None else real
+        if score not in ("sigmoid", "softmax"):
+            raise KernelError(f"moe_route: score '{score}' is neither sigmoid nor softmax")
+        if correction is not None:
+            _need(correction, "correction", torch.float32)
+            if correction.numel() != E:
+                raise KernelError("moe_route: the correction does not have one number a routed expert")
         counts = getattr(self, "_moe_counts", None)
         if counts is None or counts.device != logits.device:
             # the experts' running counts: zero between calls (the sorting kernel leaves them so), allocated once, outside any capture
@@ -662,27 +690,29 @@ class KernelLibrary:
         dev = logits.device
         wide = self._lib.roost_moe_wide_tile_rows()
         max_wide = (-(-rows // wide) + E) if rows >= MOE_TCGEN05_MIN_ROWS else 0
-        ints = torch.empty((4 * rows + (E + 1) + 3 * max_tiles + 3 * max_wide + 2 * rows,), dtype=torch.int32, device=dev)
+        ints = torch.empty((4 * rows + (E + 1) + 3 * max_tiles + 3 * max_wide + 3 * rows,), dtype=torch.int32, device=dev)
         token, expert, inverse = ints[:rows], ints[rows : 2 * rows], ints[2 * rows : 3 * rows]
         at = 3 * rows
         offsets, at = ints[at : at + E + 1], at + E + 1
         tiles, at = ints[at : at + 3 * max_tiles], at + 3 * max_tiles
         wide_tiles, at = (ints[at : at + 3 * max_wide] if max_wide else None), at + 3 * max_wide
-        scratch = ints[at : at + 2 * rows]
+        scratch = ints[at : at + 3 * rows]
         weight = torch.empty((rows,), dtype=torch.float32, device=dev)
-        self._call("roost_moe_route", _ptr(logits), T, E, top, _ptr(token), _ptr(weight), _ptr(expert), _ptr(inverse), _ptr(offsets), _ptr(tiles),
-                   max_tiles, _ptr(wide_tiles), max_wide, _ptr(scratch), _ptr(counts), _stream(), launches=2)
+        self._call("roost_moe_route", _ptr(logits), T, columns, E, real, top, 1 if score == "softmax" else 0, _ptr(correction), float(scale),
+                   _ptr(token), _ptr(weight), _ptr(expert), _ptr(inverse), _ptr(offsets), _ptr(tiles), max_tiles, _ptr(wide_tiles), max_wide,
+                   _ptr(scratch), _ptr(counts), _stream(), launches=2)
         return MoeRoute(top=top, rows=rows, token=token, weight=weight, expert=expert, inverse=inverse, offsets=offsets, tiles=tiles,
-                        max_tiles=max_tiles, form=0, wide_tiles=wide_tiles, max_wide_tiles=max_wide)
+                        max_tiles=max_tiles, form=0, real=real, wide_tiles=wide_tiles, max_wide_tiles=max_wide)
 
-    def moe_gather_scale(self, x: torch.Tensor, route: MoeRoute) -> torch.Tensor:
+    def moe_gather_scale(self, x: torch.Tensor, route: MoeRoute, scale: bool = True) -> torch.Tensor:
+        """The tokens' rows in the order of the sorted pairs, times the pair's weight (``scale``) or as they are."""
         _need(x, "x")
         xs = torch.empty((route.rows, x.shape[1]), dtype=x.dtype, device=x.device)
-        self._call("roost_moe_gather_scale", _ptr(x), _ptr(xs), _ptr(route.token), _ptr(route.weight), route.rows, x.shape[1], dtype_code(x.dtype),
-                   _stream())
+        self._call("roost_moe_gather_scale", _ptr(x), _ptr(xs), _ptr(route.token), _ptr(route.weight), route.rows, x.shape[1], 1 if scale else 0,
+                   dtype_code(x.dtype), _stream())
         return xs
 
-    def _moe_gemm(self, a, w1, w2, route: MoeRoute, block: int = 0) -> torch.Tensor:
+    def _moe_gemm(self, a, w1, w2, route: MoeRoute, block: int = 0, activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
         """The experts' product on tiles of rows or a warp an output. ``block`` > 0: ``w1`` is [experts, 2 n, k] with gate and
         up rows interleaved in blocks of ``block`` and ``w2`` is not looked at."""
         _need(a, "a"); _need(w1, "w1", a.dtype)
@@ -694,27 +724,28 @@ class KernelLibrary:
         form = 1 if (a.dtype == torch.bfloat16 and route.rows <= MOE_ROW_FORM_MAX_ROWS) else 0
         out = torch.empty((route.rows, N), dtype=a.dtype, device=a.device)
         self._call("roost_moe_expert_gemm", _ptr(a), _ptr(w1), _ptr(w2), _ptr(out), _ptr(route.tiles), route.max_tiles, _ptr(route.expert),
-                   route.rows, N, K, form, block, dtype_code(a.dtype), _stream())
+                   route.rows, N, K, form, block, GATE_FUNCTIONS[activation], float(limit), min(route.real, E), dtype_code(a.dtype), _stream())
         return out
 
-    def _moe_gemm_tcgen05(self, a, w, route: MoeRoute, swiglu: bool) -> torch.Tensor:
+    def _moe_gemm_tcgen05(self, a, w, route: MoeRoute, swiglu: bool, activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
         E, N, K = w.shape
         out = torch.empty((route.rows, N // 2 if swiglu else N), dtype=a.dtype, device=a.device)
         self._call("roost_gemm_tcgen05_grouped", _ptr(a), _ptr(w), _ptr(out), _ptr(route.wide_tiles), route.max_wide_tiles, route.rows, E, N, K,
-                   1 if swiglu else 0, _stream())
+                   1 if swiglu else 0, GATE_FUNCTIONS[activation], float(limit), _stream())
         return out
 
-    def moe_expert_gate_up(self, xs, gate, up, route: MoeRoute, gate_up: torch.Tensor | None = None) -> torch.Tensor:
+    def moe_expert_gate_up(self, xs, gate, up, route: MoeRoute, gate_up: torch.Tensor | None = None, activation: str = "silu",
+                           limit: float = 0.0) -> torch.Tensor:
         """silu(xs Wg[e]^T) * (xs Wu[e]^T) over the sorted rows, e the row's expert. The weights come as ``gate`` and ``up``
         [experts, ff, k], or as ``gate_up`` [experts, 2 ff, k] with an expert's gate and up rows interleaved in blocks of
         128: the layout in which the tcgen05 product of steps of many rows applies the activation to its accumulator, and
         which the other forms read as well."""
         if gate_up is None:
-            return self._moe_gemm(xs, gate, up, route)
+            return self._moe_gemm(xs, gate, up, route, activation=activation, limit=limit)
         if route.wide_tiles is not None and xs.dtype == torch.bfloat16 and xs.shape[1] % 8 == 0:
             _need(xs, "xs"); _need(gate_up, "gate_up", torch.bfloat16)
-            return self._moe_gemm_tcgen05(xs, gate_up, route, True)
-        return self._moe_gemm(xs, gate_up, None, route, block=128)
+            return self._moe_gemm_tcgen05(xs, gate_up, route, True, activation, limit)
+        return self._moe_gemm(xs, gate_up, None, route, block=128, activation=activation, limit=limit)
 
     def moe_expert_down(self, act, down, route: MoeRoute) -> torch.Tensor:
         if route.wide_tiles is not None and act.dtype == torch.bfloat16 and act.shape[1] % 8 == 0 and down.shape[1] % 8 == 0:
@@ -729,6 +760,125 @@ class KernelLibrary:
             _need(shared, "shared", ys.dtype)
         out = torch.empty((T, H), dtype=ys.dtype, device=ys.device)
         self._call("roost_moe_combine", _ptr(ys), _ptr(route.inverse), _ptr(shared), _ptr(out), T, H, route.top, dtype_code(ys.dtype), _stream())
+        return out
+
+    def moe_combine_weighted(self, ys: torch.Tensor, route: MoeRoute, x: torch.Tensor, shared: torch.Tensor | None = None,
+                             gate_logits: torch.Tensor | None = None) -> torch.Tensor:
+        """out[t] = sum_k weight_k * (the k-th chosen expert's output, or x[t] for an identity expert) + sigmoid(gate) * shared[t];
+        ``gate_logits``: float32 [T, columns] whose last column is the shared expert's gate logit (None: the gate is 1)."""
+        _need(ys, "ys"); _need(x, "x", ys.dtype)
+        T, H = x.shape
+        if shared is not None:
+            _need(shared, "shared", ys.dtype)
+        gate, stride = None, 0
+        if gate_logits is not None:
+            _need(gate_logits, "gate_logits", torch.float32)
+            gate, stride = gate_logits.data_ptr() + 4 * (gate_logits.shape[1] - 1), gate_logits.shape[1]
+        out = torch.empty((T, H), dtype=ys.dtype, device=ys.device)
+        self._call("roost_moe_combine_weighted", _ptr(ys), _ptr(route.inverse), _ptr(route.weight), _ptr(route.expert), _ptr(x), _ptr(shared),
+                   gate, stride, _ptr(out), T, H, route.top, route.real, dtype_code(ys.dtype), _stream())
+        return out
+
+    # ------------------------------------------------------------------ residual streams, gate functions
+    def stream_step(self, streams, norm_w, eps, out_dtype, read=None, y=None, mix=None, write=None, init_from=None, rows=None) -> torch.Tensor:
+        """One pass over the tokens' residual streams (float32 [T, S, width], updated in place): fresh streams from
+        ``init_from``, or the write-back x'_r = sum_s mix[s, r] x_s + write[r] y of the sublayer before (not stored when ``rows``
+        selects tokens); then the read u = sum_s read[s] x'_s (None: the plain sum) and its root-mean-square norm times
+        ``norm_w`` (float32, any offset folded in), in ``out_dtype``."""
+        _need(streams, "streams", torch.float32); _need(norm_w, "norm_w", torch.float32)
+        T, S, W = streams.shape
+        for n, t in (("read", read), ("mix", mix), ("write", write)):
+            if t is not None:
+                _need(t, n, torch.float32)
+        for n, t in (("y", y), ("init_from", init_from)):
+            if t is not None:
+                _need(t, n, out_dtype)
+                if tuple(t.shape) != (T, W):
+                    raise KernelError(f"stream_step: {n} is {tuple(t.shape)}; the streams hold {T} tokens of width {W}")
+        n_out = T
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+            n_out = rows.numel()
+        out = torch.empty((n_out, W), dtype=out_dtype, device=streams.device)
+        self._call("roost_stream_step", _ptr(streams), _ptr(y), _ptr(init_from), _ptr(mix), _ptr(write), _ptr(read), _ptr(norm_w), _ptr(rows),
+                   _ptr(out), n_out, S, W, float(eps), dtype_code(out_dtype), _stream())
+        return out
+
+    def gated_act_mul(self, x: torch.Tensor, activation: str, limit: float = 0.0, block: int = 0) -> torch.Tensor:
+        """fn(gate) * up over rows [gate | up] for the gate function ``activation`` (see ``GATE_FUNCTIONS``)."""
+        _need(x, "x")
+        T, two_i = x.shape
+        out = torch.empty((T, two_i // 2), dtype=x.dtype, device=x.device)
+        self._call("roost_gated_act_mul", _ptr(x), _ptr(out), T, two_i // 2, block, GATE_FUNCTIONS[activation], float(limit), dtype_code(x.dtype),
+                   _stream())
+        return out
+
+    # ------------------------------------------------------------------ attention with a sink
+    @staticmethod
+    def _sink_cache(k_pool, v_pool, dim, vdim):
+        """(keys' base address, values' base address, numbers between two entries) of a cache of two planes or of one."""
+        if v_pool is None:
+            if k_pool.shape[3] != dim + vdim:
+                raise KernelError("sink_attention: a cache of one plane holds entries of dim + vdim numbers")
+            return k_pool.data_ptr(), k_pool.data_ptr() + dim * k_pool.element_size(), dim + vdim
+        if k_pool.shape[3] != dim or v_pool.shape[3] != vdim or dim != vdim:
+            raise KernelError("sink_attention: a cache of two planes holds keys and values of one size")
+        return k_pool.data_ptr(), v_pool.data_ptr(), dim
+
+    def sink_attention_prepare(self, qkv, k_pool, v_pool, inv_freq, rotary_dim, positions, slot_mapping, heads, kv_heads, dim, vdim, eps,
+                               page_size) -> None:
+        _need(qkv, "qkv"); _need(k_pool, "k_pool", qkv.dtype); _need(positions, "positions", torch.int32); _need(slot_mapping, "slot_mapping", torch.int32)
+        if v_pool is not None:
+            _need(v_pool, "v_pool", qkv.dtype)
+        if rotary_dim:
+            _need(inv_freq, "inv_freq", torch.float64)
+        if qkv.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim or k_pool.shape[1] != kv_heads or k_pool.shape[2] != page_size:
+            raise KernelError("sink_attention_prepare: qkv or the pool do not fit the sizes")
+        kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
+        self._call("roost_sink_attention_prepare", _ptr(qkv), qkv.stride(0), kb, vb, entry, _ptr(inv_freq) if rotary_dim else None, _ptr(positions),
+                   _ptr(slot_mapping), qkv.shape[0], heads, kv_heads, dim, vdim, rotary_dim, float(eps) if eps else 0.0, page_size,
+                   dtype_code(qkv.dtype), _stream())
+
+    def sink_splits_for(self, tokens: int, gy: int, kv_cap: int) -> tuple[int, int]:
+        """(blocks a token's key tiles are dealt to, tiles a block): 1 when the step's blocks fill the device by themselves,
+        else as many as give two blocks an SM, up to 32 and to the tiles the bound on the requests' lengths allows, so that
+        every replay of a captured step agrees."""
+        if not self._decode_ctas:
+            self._decode_ctas = 2 * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        tiles = -(-max(kv_cap, 1) // 32)
+        splits = max(1, min(self._decode_ctas // max(tokens * gy, 1), -(-tiles // 4), 32))
+        per = -(-tiles // splits)
+        return -(-tiles // per), per
+
+    def sink_attention(self, qkv, k_pool, v_pool, positions, token_row, kv_indptr, kv_indices, heads, kv_heads, dim, vdim, scale, sink,
+                       kv_cap: int = 0) -> torch.Tensor:
+        """Attention of the step's (prepared) queries over the paged cache in 32-bit arithmetic: out [T, heads * vdim]."""
+        _need(qkv, "qkv"); _need(k_pool, "k_pool", qkv.dtype)
+        for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
+            _need(t, n, torch.int32)
+        T = qkv.shape[0]
+        kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
+        out = torch.empty((T, heads * vdim), dtype=qkv.dtype, device=qkv.device)
+        gy = kv_heads * (-(-(heads // kv_heads) // 8))
+        splits, per = self.sink_splits_for(T, gy, kv_cap) if kv_cap else (1, 1 << 24)
+        part = torch.empty((T * heads * splits * (vdim + 2),), dtype=torch.float32, device=qkv.device) if splits > 1 else None
+        self._call("roost_sink_attention", _ptr(qkv), qkv.stride(0), _ptr(out), _ptr(part), kb, vb, entry, _ptr(positions), _ptr(token_row),
+                   _ptr(kv_indptr), _ptr(kv_indices), T, heads, kv_heads, dim, vdim, k_pool.shape[2], float(scale), 1 if sink else 0, splits, per,
+                   dtype_code(qkv.dtype), _stream(), launches=2 if splits > 1 else 1)
+        return out
+
+    # ------------------------------------------------------------------ the selective scan
+    def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, n_state, dt_rank) -> torch.Tensor:
+        _need(xc, "xc"); _need(dt, "dt", torch.float32); _need(dbc, "dbc", xc.dtype); _need(xz, "xz", xc.dtype); _need(state, "state", torch.float32)
+        for n, t in (("dt_bias", dt_bias), ("A", a), ("D", d)):
+            _need(t, n, torch.float32)
+        T = xc.shape[0]
+        if tuple(dt.shape) != (T, inner) or tuple(a.shape) != (inner, n_state) or xc.shape[1] != inner:
+            raise KernelError("mamba1_scan: the step sizes, the decays or the convolution's output do not fit")
+        out = torch.empty((T, inner), dtype=xc.dtype, device=xc.device)
+        self._call("roost_mamba1_scan", _ptr(xc), _ptr(dt), _ptr(dbc), dbc.stride(0), _ptr(xz), xz.stride(0), _ptr(out), _ptr(dt_bias), _ptr(a),
+                   _ptr(d), _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), T, inner, n_state, dt_rank,
+                   dtype_code(xc.dtype), _stream())
         return out
 
     def attention_set_decode_tma(self, on: bool) -> None:

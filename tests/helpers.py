@@ -26,7 +26,7 @@ def make_model(model_dir, dtype, backend: str):
         from tests.fake_kernels import FakeKernels
         rt = Runtime(dtype, "cpu", FakeKernels())
     model = Model(spec, rt)
-    allow = ("lm_head.weight",) if spec.tie_embeddings else ()
+    allow = (("lm_head.weight",) if spec.tie_embeddings else ()) + tuple(spec.ignorable_tensors)
     model.load(loader.load_checkpoint(model_dir, parameter_declarations(spec), spec.weight_names, allow_unexpected=allow))
     return model
 
