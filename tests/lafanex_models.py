@@ -2,7 +2,8 @@
 show, and a recorder of the engine's routing decisions.
 
 Weights: matrices N(0, std) scaled by their fan-in; norm weights around zero (the design adds one); the streams' read weights
-around 1/S, mix matrices near the identity, write weights around one; the scan's A_log and dt bias so that a state lives for
+around 1/S, mix matrices near the identity, write weights around one; output projections small beside the residual, so that
+a layer's rounding error is not doubled by the next one; the scan's A_log and dt bias so that a state lives for
 hundreds of tokens (a lost or misplaced state changes every later logit); router rows that spread the scores; a correction
 large enough to change choices. ``sharpen`` makes one query token of the first layer score one key token far above all
 others, so that whether that key is seen decides the output.
@@ -133,6 +134,8 @@ def draw_tensors(cfg, seed: int, std: float = 0.25) -> dict:
             t = 0.05 * r
         elif name == "embed":
             t = r
+        elif name.endswith(".o") or name.endswith(".down"):
+            t = 0.25 * std * r * (32.0 / max(shape[-1], 1)) ** 0.5      # branches smaller than the residual: rounding does not compound from layer to layer
         else:
             t = std * r * (32.0 / max(shape[-1], 1)) ** 0.5
         out[name] = t.to(torch.bfloat16)
@@ -160,6 +163,10 @@ def sharpen(cfg, tensors: dict, key_token: int, query_token: int) -> None:
         k[:rot] = 0.0
         q[h] = q[h] * 0.05 + torch.outer(k / k.norm(), xq) * (8.0 / float(xq @ xq))
     tensors["l0.mix.q"] = q.reshape(w["l0.mix.q"].shape).to(torch.bfloat16)
+    # ... and the key token's value is large, so that seeing it moves the layer's output by much
+    g = torch.Generator().manual_seed(key_token)
+    direction = torch.randn(w["l0.mix.v"].shape[0], generator=g, dtype=torch.float64)
+    tensors["l0.mix.v"] = (w["l0.mix.v"] + torch.outer(20.0 * direction / direction.norm(), x[0]) / float(x[0] @ x[0])).to(torch.bfloat16)
 
 
 def write_model(model_dir, cfg, tensors) -> Path:

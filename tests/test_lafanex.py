@@ -26,9 +26,13 @@ BACKENDS = [
     pytest.param(("gpu", torch.bfloat16), id="gpu-bf16", marks=pytest.mark.gpu),
     pytest.param(("fake", torch.float32), id="cpu-fake"),
 ]
-F32_WORST, F32_RMS = 1e-3, 2e-5     # a fault moves the root mean square by orders of magnitude more; the worst of thousands of logits is one ill-conditioned token
-BF16_WORST, BF16_RMS = 0.5, 0.05     # the worst of tens of thousands of logits is the tail of the rounding noise; the root mean square is what a fault moves
-ROUTE_SLACK = 0.05                   # in choice scores (softmax scores plus the correction): what bfloat16 inputs may move a score by
+# Two bounds: the root-mean-square error of all logits of a request, and the largest root-mean-square error of one position's
+# logits (both relative to the logits' own root mean square). A fault that strikes one position (a lost key, a wrong page or
+# slot in one step) moves that position's logits by tens of percent and barely shows among hundreds of positions; rounding
+# alone stays far below both bounds (measured: float32 5e-6 and 3e-5, bfloat16 0.01 to 0.05 and up to 0.15).
+F32_TOKEN, F32_RMS = 1e-3, 2e-5
+BF16_TOKEN, BF16_RMS = 0.3, 0.06
+ROUTE_SLACK = 0.2                    # in choice scores (softmax scores plus the correction): what bfloat16 inputs may move a score by
 
 
 @pytest.fixture(params=BACKENDS)
@@ -86,19 +90,25 @@ class Run:
     def finish(self, rid):
         self.ex.finish(rid)
 
-    def check(self, rid, ids, weights, what, bf16_bounds=(BF16_WORST, BF16_RMS), slack=ROUTE_SLACK, f32_bounds=(F32_WORST, F32_RMS)):
+    def check(self, rid, ids, weights, what, bf16_bounds=(BF16_TOKEN, BF16_RMS), slack=ROUTE_SLACK, f32_bounds=(F32_TOKEN, F32_RMS)):
         got = torch.cat(self.logits.pop(rid))
         forced = {run: torch.cat(v) for run, v in self.forced.pop(rid, {}).items()} if self.record else None
         n = got.shape[0]
         want = P.forward(self.cfg, weights, list(ids[:n]), forced=forced, slack=slack)
-        err, rms = H.scaled_error(got, want), H.rms_error(got, want)
-        print(f"MEASURED {what} {self.dtype}: worst scaled error {err:.3e}, rms error {rms:.3e}")
+        err, rms = token_error(got, want), H.rms_error(got, want)
+        print(f"MEASURED {what} {self.dtype}: worst position's error {err:.3e}, rms error {rms:.3e}")
         worst, bound = f32_bounds if self.dtype == torch.float32 else bf16_bounds
-        assert err < worst and rms < bound, f"{what}: worst scaled error {err}, rms error {rms}"
+        assert err < worst and rms < bound, f"{what}: worst position's error {err}, rms error {rms}"
         return got, want
 
     def all_free(self):
         return all(p.used_count == 0 for p in self.ex.cache.pools)
+
+
+def token_error(got, want) -> float:
+    """The largest error of one position: root mean square of its logits' differences over that of its logits."""
+    got, want = got.double().cpu(), want.double().cpu()
+    return float(((got - want).pow(2).mean(-1).sqrt() / want.pow(2).mean(-1).sqrt()).max())
 
 
 def ids_for(cfg, n, seed):
@@ -272,7 +282,9 @@ def test_a_key_far_away_among_hundreds_at_every_page_offset(tmp_path_factory, ba
         got, want = run.check(rid, ids, weights, f"far key at {at}")
         seen[at] = want[321]
     for at in (0, 1, 2, 3, 31, 32, 33):
-        assert H.rms_error(seen[at][None], seen[None][None]) > 0.1
+        moved = H.rms_error(seen[at][None], seen[None][None])
+        print(f"MEASURED the key at {at} moves the query's logits by {moved:.3f}")
+        assert moved > 2 * BF16_TOKEN
 
 
 def test_the_first_tokens_of_a_sequence_one_by_one(any_model, backend):
