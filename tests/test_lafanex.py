@@ -32,7 +32,7 @@ BACKENDS = [
 # alone stays far below both bounds (measured: float32 5e-6 and 3e-5, bfloat16 0.01 to 0.05 and up to 0.15).
 F32_TOKEN, F32_RMS = 1e-3, 2e-5
 BF16_TOKEN, BF16_RMS = 0.3, 0.06
-ROUTE_SLACK = 0.2                    # in choice scores (softmax scores plus the correction): what bfloat16 inputs may move a score by
+ROUTE_SLACK = 0.35                   # in choice scores (softmax scores plus the correction): what bfloat16 inputs may move a score by
 
 
 @pytest.fixture(params=BACKENDS)

@@ -191,10 +191,10 @@ def test_routing_chooses_the_largest_scores_and_sorts_the_pairs_by_expert(kernel
     for form in (0, 1):
         a = torch.empty(T * top, ff, dtype=dtype, device="cuda")
         kernels._call("roost_moe_expert_gemm", xs.data_ptr(), wg.data_ptr(), wu.data_ptr(), a.data_ptr(), route.tiles.data_ptr(), route.max_tiles,
-                      route.expert.data_ptr(), T * top, ff, hidden, form, 0, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
+                      route.expert.data_ptr(), T * top, ff, hidden, form, 0, 0, 0.0, 1 << 30, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
         y = torch.empty(T * top, hidden, dtype=dtype, device="cuda")
         kernels._call("roost_moe_expert_gemm", a.data_ptr(), wd.data_ptr(), None, y.data_ptr(), route.tiles.data_ptr(), route.max_tiles,
-                      route.expert.data_ptr(), T * top, hidden, ff, form, 0, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
+                      route.expert.data_ptr(), T * top, hidden, ff, form, 0, 0, 0.0, 1 << 30, 0 if dtype == torch.float32 else 1, torch.cuda.current_stream().cuda_stream)
         outs.append(kernels.moe_combine(y, route, shared))
     want = shared.double().cpu().clone()
     xd = x.double().cpu()
