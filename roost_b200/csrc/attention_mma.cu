@@ -365,6 +365,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
                                                                 const int32_t* __restrict__ kv_indptr,
                                                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
                                                                 int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
+  const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // one more term, 2^(0 - m), in every row's denominator
+  window &= ~ROOST_ATTENTION_SINK;
   constexpr int BM = 64 * MT, BN = 64, HALF = 32, NT = 128;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -453,7 +455,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
     for (int r = 0; r < 2; ++r) {
       const int pr = row0 + warp * 16 * MT + mt * 16 + (lane >> 2) + r * 8;
       if (pr >= rows_total) continue;
-      const float inv = st.l[mt][r] > 0.f ? 1.0f / st.l[mt][r] : 0.f;
+      const float lr = st.l[mt][r] + sink * exp2f(-(st.m[mt][r] == -INFINITY ? 0.f : st.m[mt][r]));
+      const float inv = lr > 0.f ? 1.0f / lr : 0.f;
       __nv_bfloat16* dst = out + ((size_t)(q_start + pr / group) * q_heads + kvh * group + pr % group) * D + (lane & 3) * 2;
 #pragma unroll
       for (int nn = 0; nn < D / 8; ++nn) {
@@ -478,6 +481,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
                             const int32_t* __restrict__ kv_indices, const int4* __restrict__ work, float* __restrict__ part_o,
                             float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window,
                             int slot_limit) {
+  const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // added where a row's result is final, never to a partial one
+  window &= ~ROOST_ATTENTION_SINK;
   constexpr int BN = kDecodeTileKeys, STAGES = kDecodeStages;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -599,6 +604,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
       o += sm_o[((size_t)ww * 16 + row) * D + col] * f;
     }
     if (slot < 0) {
+      l += sink * exp2f(-msafe);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       out[((size_t)(q_start + row / group) * q_heads + kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
     } else {
@@ -682,6 +688,8 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
                                 const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices,
                                 const int4* __restrict__ work, int items, float* __restrict__ part_o, float* __restrict__ part_ml, int q_heads,
                                 int kv_heads, int page_size, float scale_log2, int window, int cluster_chunks) {
+  const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // added where a row's result is final, never to a partial one
+  window &= ~ROOST_ATTENTION_SINK;
   // cluster_chunks = S > 0: the grid is clusters of S CTAs, one cluster a (row, key/value head), the row's work items S in
   // a row of the list (some of them empty); CTA r of a cluster takes the r-th, leaves its result in its own shared memory
   // and the CTAs combine the S results in chunk order, with the merge kernel's arithmetic, through distributed shared
@@ -1018,6 +1026,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
             cl_o[16 * D + row * 2 + 1] = l;
           }
         } else if (c.slot < 0) {
+          l += sink * exp2f(-msafe);
           const float inv = l > 0.f ? 1.0f / l : 0.f;
           out[((size_t)(c.q_start + row / group) * q_heads + c.kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
         } else {
@@ -1073,6 +1082,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
             o += po[cc] * f;
           }
         }
+        l += sink * exp2f(-msafe);
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         out[((size_t)(cl_q_start + row / group) * q_heads + cl_kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
       }
@@ -1097,7 +1107,7 @@ constexpr int kMergeAhead = 9;  // chunks whose partial results a merge thread l
 // merge_work[i] = (batch row, first partial slot, number of chunks | packed rows << 24, the row's first token)
 template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       const int4* __restrict__ merge_work, int q_heads, int kv_heads, int slot_limit) {
+                                       const int4* __restrict__ merge_work, int q_heads, int kv_heads, int slot_limit, float sink) {
   pdl_launch_dependents(5);
   const int4 w = merge_work[blockIdx.x];  // the step's work lists are on the device before the step's first kernel runs
   const int b = w.x, slot0 = w.y, chunks = w.z & 0xffffff, rows_total = w.z >> 24, q_start = w.w;
@@ -1152,6 +1162,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
           for (int j = 0; j < (D + 127) / 128; ++j) o[j] += po[j][c] * f;
         }
       }
+      l += sink * exp2f(-msafe);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
       for (int j = 0; j < (D + 127) / 128; ++j) {
@@ -1173,6 +1184,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
         l += part_ml[pr * 2 + 1] * f;
         o += part_o[pr * D + col] * f;
       }
+      l += sink * exp2f(-msafe);
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       out[out_at + col] = __float2bfloat16_rn(o * inv);
     }
@@ -1313,7 +1325,8 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
   if (rc != ROOST_OK || merge_items == 0) return rc;
   const int rows = merge_rows < 1 ? 1 : (merge_rows > 16 ? 16 : merge_rows);  // blocks along z; each walks the rows beyond
   launch_kernel(attention_merge_kernel<D>, dim3(merge_items, kv_heads, rows), dim3(D < 128 ? D : 128), 0, s, (__nv_bfloat16*)out,
-                (const float*)part_o, (const float*)part_ml, (const int4*)merge_work, q_heads, kv_heads, slot_limit);
+                (const float*)part_o, (const float*)part_ml, (const int4*)merge_work, q_heads, kv_heads, slot_limit,
+                (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f);
   return check_launch("attention_merge");
 }
 

@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(64 + NG * 128, 1)
                                 const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ kv_indptr,
                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work, int items, int q_heads, int kv_heads,
                                 int page_size, float scale_log2, int window) {
+  const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // one more term, 2^(0 - m), in every row's denominator
+  window &= ~ROOST_ATTENTION_SINK;
   using Cfg = TcCfg<D, NG>;
   constexpr int BM = kTcRows, TK = kTcKeys, KS = Cfg::kKStages, VS = Cfg::kVStages, NP = TK / RPC, CB = D / 64;
   constexpr uint32_t kQBytes = BM * D * 2;                  // one row group's Q tile
@@ -451,6 +453,7 @@ __global__ void __launch_bounds__(64 + NG * 128, 1)
       if (ok && my_tiles > 0) ok = mbar_wait_limited(o_done(g), (uint32_t)outs & 1u, abortp, 8, &g_attention_tc_error);
       if (ok && my_tiles > 0) {
         tcgen05_fence_after();
+        l += sink * ex2(-(m == -INFINITY ? 0.f : m));
         const float inv = l > 0.f ? 1.0f / l : 0.f;
         __nv_bfloat16* dst = valid ? out + ((size_t)(p.q_start + pr / group) * q_heads + p.kvh * group + pr % group) * D : nullptr;
 #pragma unroll 1

@@ -33,6 +33,10 @@ extern "C" {
 #define ROOST_ACT_GELU_TANH 1
 #define ROOST_ACT_CLAMPED_SWISH 2
 
+/* Added to the `window` argument of the tensor-core attention entry points (roost_attention_prefill, _decode, _decode_cluster,
+ * _decode_static): the softmax's denominator gets one more term, exp(0 - maximum), a key of score 0 that has no value. */
+#define ROOST_ATTENTION_SINK (1 << 30)
+
 typedef void* roost_stream_t;
 
 int roost_abi_version(void);
@@ -356,9 +360,9 @@ int roost_gated_act_mul(const void* x, void* out, int tokens, int inter, int blo
 
 /* ---- attention with a sink, unit-norm heads and values of their own size (sink_attention.cu) ---- */
 /* qkv rows [q heads | k heads | v heads] with row stride ld: rotation of interleaved pairs and unit root mean square (eps <= 0:
- * none) on q (in place) and k; k and v to the cache entry of the token's slot: ((page * kv_heads + head) * page_size + offset) *
+ * none) on q (in place, or to the dense [tokens, heads, dim] q_out when it is given) and k; k and v to the cache entry of the token's slot: ((page * kv_heads + head) * page_size + offset) *
  * entry from k_base and v_base. */
-int roost_sink_attention_prepare(void* qkv, int64_t ld, void* k_base, void* v_base, int entry, const double* inv_freq,
+int roost_sink_attention_prepare(void* qkv, int64_t ld, void* q_out, void* k_base, void* v_base, int entry, const double* inv_freq,
                                  const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int kv_heads, int dim, int vdim,
                                  int rot_dims, float eps, int page_size, int dtype, roost_stream_t stream);
 /* out [tokens, heads * vdim]. sink != 0: one is added to the softmax's denominator. splits > 1: a token's key tiles of 32 are

@@ -4,7 +4,8 @@
 //   prepare:   per token, on a row [q heads | k heads | v heads] of the fused projection: every query and key head has its
 //              first rot_dims elements turned in interleaved pairs, (u, v) at (2i, 2i+1) -> (u cos a - v sin a, v cos a + u sin a)
 //              with a = position * inv_freq[i] formed in double and reduced to [-pi, pi]; then, with eps > 0, the head is
-//              divided by sqrt(mean(x^2) + eps) (no weight). Queries are written back in place, keys and values go to the
+//              divided by sqrt(mean(x^2) + eps) (no weight). Queries are written back in place (or, with q_out, to a dense
+//              [tokens, heads, dim] tensor of their own, which the tensor-core attention kernels read), keys and values go to the
 //              token's cache slot (slot -1: nothing is written). The cache entry of (page, kv head, offset) starts at
 //              ((page * kv_heads + head) * page_size + offset) * entry from k_base (keys) and v_base (values): two planes of one
 //              size, or one plane whose entries are [key | value] (v_base = k_base + dim, entry = dim + vdim).
@@ -23,7 +24,7 @@ constexpr int kSaWarps = 8;
 constexpr int kSaMaxDim = 512;
 
 template <typename T>
-__global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T* k_base, T* v_base, int entry, const double* __restrict__ inv_freq,
+__global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T* q_out, T* k_base, T* v_base, int entry, const double* __restrict__ inv_freq,
                                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
                                                           int heads, int kv_heads, int dim, int vdim, int rot_dims, float eps, int page_size) {
   extern __shared__ float sm[];      // rot_dims/2 cosines, rot_dims/2 sines
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T
     }
     ss = warp_sum(ss);
     const float inv = eps > 0.f ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;
-    T* dst = x;
+    T* dst = q_out != nullptr ? q_out + ((size_t)t * heads + h) * dim : x;
     if (h >= heads) {
       if (slot < 0) continue;          // a padding token: no key is written
       dst = k_base + ((page * kv_heads + (h - heads)) * page_size + off) * entry;
@@ -226,7 +227,7 @@ __global__ void sink_merge_kernel(const float* __restrict__ part, T* __restrict_
 
 using namespace roost;
 
-extern "C" int roost_sink_attention_prepare(void* qkv, int64_t ld, void* k_base, void* v_base, int entry, const double* inv_freq,
+extern "C" int roost_sink_attention_prepare(void* qkv, int64_t ld, void* q_out, void* k_base, void* v_base, int entry, const double* inv_freq,
                                             const int32_t* positions, const int32_t* slot_mapping, int tokens, int heads, int kv_heads, int dim,
                                             int vdim, int rot_dims, float eps, int page_size, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0 && page_size > 0, "sink_attention_prepare: sizes must be positive");
@@ -237,7 +238,7 @@ extern "C" int roost_sink_attention_prepare(void* qkv, int64_t ld, void* k_base,
   if (dim > kSaMaxDim) return fail(ROOST_ERR_UNSUPPORTED, "sink_attention_prepare: heads beyond 512 numbers");
   if (tokens == 0) return ROOST_OK;
   const size_t smem = ((size_t)rot_dims + 2) * sizeof(float);
-  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(sink_prepare_kernel<T>, dim3(tokens), dim3(128), smem, (cudaStream_t)stream, (T*)qkv, ld, (T*)k_base,
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(sink_prepare_kernel<T>, dim3(tokens), dim3(128), smem, (cudaStream_t)stream, (T*)qkv, ld, (T*)q_out, (T*)k_base,
                                                (T*)v_base, entry, inv_freq, positions, slot_mapping, heads, kv_heads, dim, vdim, rot_dims, eps,
                                                page_size));
   return check_launch("sink_attention_prepare");

@@ -137,7 +137,7 @@ _SIGNATURES = {
     "roost_stream_step": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                           c_int, c_void_p],
     "roost_gated_act_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
-    "roost_sink_attention_prepare": [c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+    "roost_sink_attention_prepare": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                      c_int, c_float, c_int, c_int, c_void_p],
     "roost_sink_attention": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
@@ -365,16 +365,20 @@ class KernelLibrary:
         """Prompt portions run the tcgen05 attention kernel where the sizes allow (the default), or never."""
         self._lib.roost_attention_set_prefill_tc(1 if on else 0)
 
+    attention_mma_sink = True    # the tensor-core kernels take a softmax with one added to its denominator (``sink``)
+    ATTENTION_SINK = 1 << 30     # ROOST_ATTENTION_SINK of csrc/roost_kernels.h
+
     def attention_mma(self, q, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, plan, scale: float,
-                      window: int | None) -> torch.Tensor:
-        """Tensor-core attention (bfloat16). ``plan``: an ``AttentionPlan`` whose work lists are on the device."""
+                      window: int | None, sink: bool = False) -> torch.Tensor:
+        """Tensor-core attention (bfloat16). ``plan``: an ``AttentionPlan`` whose work lists are on the device. ``sink``: one is
+        added to the softmax's denominator (a key of score 0 that has no value)."""
         _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16)
         T, nq, d = q.shape
         _, nkv, page, d2 = k_pool.shape
         if d2 != d:
             raise KernelError("attention_mma: head_dim of q and of the pool differ")
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
-        w = int(window) if window else 0
+        w = (int(window) if window else 0) | (self.ATTENTION_SINK if sink else 0)
         if plan.prefill_items:
             self._call("roost_attention_prefill", _ptr(q), T, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
                        _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page,
@@ -826,7 +830,12 @@ class KernelLibrary:
         return k_pool.data_ptr(), v_pool.data_ptr(), dim
 
     def sink_attention_prepare(self, qkv, k_pool, v_pool, inv_freq, rotary_dim, positions, slot_mapping, heads, kv_heads, dim, vdim, eps,
-                               page_size) -> None:
+                               page_size, q_out: torch.Tensor | None = None) -> None:
+        """``q_out`` [tokens, heads, dim]: where the prepared queries go instead of back into ``qkv``."""
+        if q_out is not None:
+            _need(q_out, "q_out", qkv.dtype)
+            if tuple(q_out.shape) != (qkv.shape[0], heads, dim):
+                raise KernelError("sink_attention_prepare: q_out is not [tokens, heads, dim]")
         _need(qkv, "qkv"); _need(k_pool, "k_pool", qkv.dtype); _need(positions, "positions", torch.int32); _need(slot_mapping, "slot_mapping", torch.int32)
         if v_pool is not None:
             _need(v_pool, "v_pool", qkv.dtype)
@@ -835,7 +844,7 @@ class KernelLibrary:
         if qkv.shape[1] != (heads + kv_heads) * dim + kv_heads * vdim or k_pool.shape[1] != kv_heads or k_pool.shape[2] != page_size:
             raise KernelError("sink_attention_prepare: qkv or the pool do not fit the sizes")
         kb, vb, entry = self._sink_cache(k_pool, v_pool, dim, vdim)
-        self._call("roost_sink_attention_prepare", _ptr(qkv), qkv.stride(0), kb, vb, entry, _ptr(inv_freq) if rotary_dim else None, _ptr(positions),
+        self._call("roost_sink_attention_prepare", _ptr(qkv), qkv.stride(0), _ptr(q_out), kb, vb, entry, _ptr(inv_freq) if rotary_dim else None, _ptr(positions),
                    _ptr(slot_mapping), qkv.shape[0], heads, kv_heads, dim, vdim, rotary_dim, float(eps) if eps else 0.0, page_size,
                    dtype_code(qkv.dtype), _stream())
 

@@ -71,20 +71,21 @@ class SinkAttention(Mixer):
         tables = batch.groups[cache.group]
         inv_freq, rotary_dim = self.position.rotation() if self.position is not None else (None, 0)
         qkv = self.qkv(x)
+        tensor_cores = (self.two_planes and qkv.dtype == torch.bfloat16 and getattr(k, "attention_mma_sink", False)
+                        and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim))
+        q = torch.empty((qkv.shape[0], s.num_heads, s.head_dim), dtype=qkv.dtype, device=qkv.device) if tensor_cores else None
         k.sink_attention_prepare(qkv, cache.k_pool, cache.v_pool, inv_freq, rotary_dim, batch.positions, tables.slot_mapping, s.num_heads,
-                                 s.num_kv_heads, s.head_dim, s.v_dim, s.unit_norm_eps, cache.page_size)
-        if (self.two_planes and qkv.dtype == torch.bfloat16 and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim)
-                and getattr(k, "attention_mma_sink", False)):
-            o = self._attend_tensor_cores(qkv, batch, cache, tables)
+                                 s.num_kv_heads, s.head_dim, s.v_dim, s.unit_norm_eps, cache.page_size, **({"q_out": q} if tensor_cores else {}))
+        if tensor_cores:
+            o = self._attend_tensor_cores(q, batch, cache, tables)
         else:
             o = k.sink_attention(qkv, cache.k_pool, cache.v_pool, batch.positions, batch.token_row, tables.kv_indptr, tables.kv_indices,
                                  s.num_heads, s.num_kv_heads, s.head_dim, s.v_dim, s.scale, s.sink, kv_cap=batch.kv_cap)
         return self.out(o)
 
     # ---- bfloat16 with keys and values of one size: the framework's tensor-core kernels, with the sink
-    def _attend_tensor_cores(self, qkv, batch, cache, tables):
+    def _attend_tensor_cores(self, q, batch, cache, tables):
         s, k = self.spec, self.rt.kernels
-        q = qkv[:, : self.q_width]
         group = s.num_heads // s.num_kv_heads
         tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group)
         split_for = getattr(k, "decode_split_for", None)

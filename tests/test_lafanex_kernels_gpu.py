@@ -265,3 +265,57 @@ def test_expert_products_with_the_clamped_swish_skip_identity_rows(kernels, dtyp
         sel = expert == e
         want[sel] = P.clamped_expert(xs.cpu().double()[sel], w, f"e{e}.", limit)
     close(ys[real.cuda()], want[real], dtype, "experts with the clamped swish", bf16=4e-2)
+
+
+# ------------------------------------------------------------------------------------------------ the sink on the tensor cores
+@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (128, 8, 2), (32, 2, 2)])
+def test_the_tensor_core_attention_kernels_with_a_sink_against_the_32_bit_kernel(tmp_path, kernels, dim, heads, kv_heads):
+    """A one-layer model whose keys and values have one size runs its bfloat16 attention on the framework's tensor-core
+    kernels with the sink added at their ends: a prompt of 700 tokens (the tcgen05 or mma.sync prefill), portions, three
+    requests decoding side by side beyond 512 keys (split rows merged by clusters or by the merge kernel) and one short one.
+    The same steps with that path switched off run the 32-bit kernel; both are held against the plain implementation."""
+    from roost_b200.engine.executor import StepEntry, StepExecutor
+    from tests import lafanex_models as LM
+    cfg = LM.config([(LM.attention(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, rot=dim // 2, base=10000.0, scale=2.0 / dim), None)],
+                    width=64, vocab=90, streams=2)
+    tensors = LM.draw_tensors(cfg, seed=dim)
+    folder = LM.write_model(tmp_path / "m", cfg, tensors)
+    weights = LM.plain_weights(tensors)
+    reqs = {"a": H.random_ids(760, 90, 1), "b": H.random_ids(600, 90, 2), "c": H.random_ids(530, 90, 3), "d": H.random_ids(9, 90, 4)}
+    results = {}
+    for tensor_cores in (True, False):
+        model = H.make_model(folder, torch.bfloat16, "gpu")
+        if not tensor_cores:
+            model.rt.kernels.attention_mma_sink = False
+        try:
+            ex = StepExecutor(model, page_size=16, num_pages=140, max_requests=4)
+            outs = {r: [] for r in reqs}
+
+            def step(entries):
+                logits = ex.step([StepEntry(r, list(t), list(range(len(t)))) for r, t in entries])
+                at = 0
+                for r, t in entries:
+                    outs[r].append(logits[at : at + len(t)].float().cpu())
+                    at += len(t)
+
+            step([("a", reqs["a"][:700])])
+            step([("b", reqs["b"][:300]), ("a", reqs["a"][700:720])])
+            step([("b", reqs["b"][300:570]), ("c", reqs["c"][:520]), ("d", reqs["d"][:3])])
+            at = {"a": 720, "b": 570, "c": 520, "d": 3}
+            for _ in range(6):
+                step([(r, reqs[r][at[r] : at[r] + 1]) for r in reqs])
+                for r in reqs:
+                    at[r] += 1
+            results[tensor_cores] = {r: torch.cat(v) for r, v in outs.items()}
+        finally:
+            if not tensor_cores:
+                del model.rt.kernels.attention_mma_sink
+        model.rt.kernels.check_device_status()
+    for r, ids in reqs.items():
+        n = results[True][r].shape[0]
+        want = P.forward(cfg, weights, ids[:n])
+        for tensor_cores in (True, False):
+            rms = H.rms_error(results[tensor_cores][r], want)
+            print(f"MEASURED head size {dim} request {r} tensor cores {tensor_cores}: rms error {rms:.3e}")
+            assert rms < 0.02, (r, tensor_cores, rms)
+        assert H.rms_error(results[True][r], results[False][r]) < 0.02
