@@ -268,17 +268,27 @@ def test_expert_products_with_the_clamped_swish_skip_identity_rows(kernels, dtyp
 
 
 # ------------------------------------------------------------------------------------------------ the sink on the tensor cores
+@pytest.mark.parametrize("faint", [False, True], ids=["random scores", "faint scores"])
 @pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (128, 8, 2), (32, 2, 2)])
-def test_the_tensor_core_attention_kernels_with_a_sink_against_the_32_bit_kernel(tmp_path, kernels, dim, heads, kv_heads):
+def test_the_tensor_core_attention_kernels_with_a_sink_against_the_32_bit_kernel(tmp_path, kernels, dim, heads, kv_heads, faint):
     """A one-layer model whose keys and values have one size runs its bfloat16 attention on the framework's tensor-core
     kernels with the sink added at their ends: a prompt of 700 tokens (the tcgen05 or mma.sync prefill), portions, three
     requests decoding side by side beyond 512 keys (split rows merged by clusters or by the merge kernel) and one short one.
-    The same steps with that path switched off run the 32-bit kernel; both are held against the plain implementation."""
+    The same steps with that path switched off run the 32-bit kernel; both are held against the plain implementation.
+    With random weights the sink's one is lost among hundreds of keys, so a second set of weights makes it count at every
+    length: all tokens' embeddings nearly alike and every key the negative of its group's first query, so that every score of
+    those heads is near -6 and seven hundred keys weigh about as much as the sink."""
     from roost_b200.engine.executor import StepEntry, StepExecutor
     from tests import lafanex_models as LM
-    cfg = LM.config([(LM.attention(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, rot=dim // 2, base=10000.0, scale=2.0 / dim), None)],
-                    width=64, vocab=90, streams=2)
+    cfg = LM.config([(LM.attention(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, rot=2 if faint else dim // 2, base=10000.0,
+                                   scale=(6.0 if faint else 2.0) / dim), None)], width=64, vocab=90, streams=2)
     tensors = LM.draw_tensors(cfg, seed=dim)
+    if faint:
+        g = torch.Generator().manual_seed(5)
+        tensors["embed"] = (torch.randn(64, generator=g)[None, :] + 0.1 * torch.randn(90, 64, generator=g)).to(torch.bfloat16)
+        q = tensors["l0.mix.q"].reshape(heads, dim, 64)
+        tensors["l0.mix.k"] = (-q[:: heads // kv_heads]).reshape(kv_heads * dim, 64).contiguous()
+        tensors["l0.mix.o"] = tensors["l0.mix.o"] * 32          # the attention's output decides the logits
     folder = LM.write_model(tmp_path / "m", cfg, tensors)
     weights = LM.plain_weights(tensors)
     reqs = {"a": H.random_ids(760, 90, 1), "b": H.random_ids(600, 90, 2), "c": H.random_ids(530, 90, 3), "d": H.random_ids(9, 90, 4)}
@@ -319,3 +329,28 @@ def test_the_tensor_core_attention_kernels_with_a_sink_against_the_32_bit_kernel
             print(f"MEASURED head size {dim} request {r} tensor cores {tensor_cores}: rms error {rms:.3e}")
             assert rms < 0.02, (r, tensor_cores, rms)
         assert H.rms_error(results[True][r], results[False][r]) < 0.02
+    if faint:       # the test's own sharpness: without the sink the last position's logits of the longest request are far off
+        import copy
+        from tests.plain import lafanex_plain as plain
+        orig = plain.sink_attention
+        try:
+            def no_sink(h, w, p, m, eps, positions=None):
+                T = h.shape[0]
+                qq = plain.unit_rms(plain.rotate_pairs((h @ w[p + "q"].T).reshape(T, heads, dim), list(range(T)), m["rot"]["dims"], m["rot"]["base"]), eps)
+                kk = plain.unit_rms(plain.rotate_pairs((h @ w[p + "k"].T).reshape(T, kv_heads, dim), list(range(T)), m["rot"]["dims"], m["rot"]["base"]), eps)
+                vv = (h @ w[p + "v"].T).reshape(T, kv_heads, dim)
+                out = torch.zeros(T, heads, dim, dtype=torch.float64)
+                for hh in range(heads):
+                    sc = (qq[:, hh] @ kk[:, hh // (heads // kv_heads)].T) * m["scale"]
+                    sc = sc.masked_fill(~torch.tril(torch.ones(T, T, dtype=torch.bool)), float("-inf"))
+                    out[:, hh] = torch.softmax(sc, -1) @ vv[:, hh // (heads // kv_heads)]
+                return out.reshape(T, heads * dim) @ w[p + "o"].T
+            plain.sink_attention = no_sink
+            without = plain.forward(cfg, weights, reqs["a"][:726])
+        finally:
+            plain.sink_attention = orig
+        want_last = P.forward(cfg, weights, reqs["a"][:726])[-1:]
+        moved = H.rms_error(without[-1:], want_last)
+        errs = [H.rms_error(results[tc]["a"][-1:], want_last) for tc in (True, False)]
+        print(f"MEASURED without the sink the last position's logits move by {moved:.4f}; the kernels' errors there: {errs[0]:.2e}, {errs[1]:.2e}")
+        assert moved > 8 * max(errs)
