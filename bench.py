@@ -3,6 +3,7 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl reference]
     python bench.py --sizes 0.6b|8b|32b          the same line at another model's layer sizes
     python bench.py --workload serving --sizes 0.6b [--requests 32] [--budget 512] [--new-tokens 256] [--max-prompt 2048]
+    python bench.py --workload designs [--design vamatar|lafanex]      the other designs' models beside models of equal size
 
 Prints ONE JSON line. ``value`` is decoded tokens per second over K timed decode steps of ``--batch`` requests
 that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e`` is the same through the
@@ -377,9 +378,74 @@ def build_vamatar(sizes: dict, dtype, seed: int = 0):
     return model, cfg
 
 
+# Lafanex models at the same widths, depths, vocabularies and expert sizes: an attention with a sink (keys and values of one
+# size: the tensor-core kernels) in every fourth layer, selective scans between (2 x width channels, a state of 16), routed
+# experts with two identity experts and a gated shared one everywhere but the first layer, four residual streams.
+def _lafanex_config(width, heads, dim, experts, top, ff, shared, dense_ff, layers, vocab, **_):
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                                                "rot": {"base": 1000000.0, "dims": dim}}}
+    scan = {"type": "mamba1", "mixer": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "identity": 2, "scale": 2.5}, "expert": {"ff": ff, "limit": 7.0},
+           "shared": {"ff": shared, "limit": 7.0}}
+    out = []
+    for i in range(layers):
+        if i % 4 == 0:
+            out.append(dict(attention, mlp={"kind": "dense", "ff": dense_ff} if i == 0 else moe))
+        else:
+            out.append(dict(scan, mlp=moe))
+    return {"architecture": "Lafanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "streams": 4, "layers": out}
+
+
+def build_lafanex(sizes: dict, dtype, seed: int = 0):
+    import torch
+
+    from roost_b200.config.lafanex import LafanexConfig
+    from roost_b200.engine.model import Model
+    from roost_b200.kernels import library
+    from roost_b200.parts import Runtime
+    from roost_b200.weights.random_init import random_parameters
+    cfg = _lafanex_config(**dict(sizes, dim=128 if sizes["width"] >= 2048 else 64))
+    spec = LafanexConfig.from_dict(cfg).to_spec()
+    model = Model(spec, Runtime(dtype, "cuda", library.load()))
+    model.load(random_parameters(spec, seed, torch.device("cuda"), dtype, std=0.02))
+    return model, cfg
+
+
+def lafanex_main(args) -> int:
+    """Prefill and decode throughput of Lafanex models beside Vamatar models (the closest design the engine has: attention,
+    recurrences and routed experts) of equal width, depth, vocabulary and expert sizes, one JSON line."""
+    import torch
+    pk, pk_src = peaks()
+    out = {}
+    for name in args.design_sizes.split(","):
+        s = DESIGN_SIZES[name]
+        rec = {}
+        for which in ("lafanex", "vamatar"):
+            model, _ = build_lafanex(s, torch.bfloat16) if which == "lafanex" else build_vamatar(s, torch.bfloat16)
+            r = {"weight_gb": round(model.weight_bytes() / 1e9, 3)}
+            ms = timed_prefill(model, args.prefill_tokens)
+            r["prefill"] = {"tokens": args.prefill_tokens, "ms": round(ms, 3), "tokens_per_s": round(args.prefill_tokens / ms * 1e3)}
+            for batch in _ints(args.design_batches):
+                tps, ms, launches, _ = timed_decode(model, batch, args.design_context, args.steps, max(args.warmup, 3))
+                r[f"decode_b{batch}"] = {"context": args.design_context, "ms": round(ms, 4), "tokens_per_s": round(tps), "launches": launches[0] // args.steps,
+                                         "library_launches": launches[1] // args.steps}
+            rec[which] = r
+            del model
+            gc.collect()
+            torch.cuda.empty_cache()
+        rec["config"] = s
+        out[name] = rec
+    print(json.dumps({"metric": "prefill and decode tokens/s of Lafanex models beside Vamatar models of equal width, depth, vocabulary and expert sizes",
+                      "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "impl": "ours", "peaks": pk_src,
+                      "data": "synthetic: seeded random weights, seeded random tokens; device-timed with CUDA events", "sizes": out}))
+    return 0
+
+
 def designs_main(args) -> int:
     """Prefill and decode throughput of Vamatar models beside Qwen3-shaped models of equal size, one JSON line."""
     import torch
+    if args.design == "lafanex":
+        return lafanex_main(args)
     pk, pk_src = peaks()
     out = {}
     for name in args.design_sizes.split(","):
@@ -428,6 +494,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="layers built (default: all the layers of --sizes)")
     ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="whose layer sizes: Qwen3-0.6B, -8B (the headline) or -32B")
     ap.add_argument("--design-sizes", default="w1024,w2048", help="--workload designs: which of the Vamatar layer sizes to measure")
+    ap.add_argument("--design", default="vamatar", choices=["vamatar", "lafanex"],
+                    help="--workload designs: vamatar (beside Qwen3-shaped models) or lafanex (beside Vamatar models of equal size)")
     ap.add_argument("--design-batches", default="1,8", help="--workload designs: decode batch sizes")
     ap.add_argument("--design-context", type=int, default=1024, help="--workload designs: keys every decoding request holds")
     ap.add_argument("--workload", default="decode", choices=["decode", "serving", "designs"],

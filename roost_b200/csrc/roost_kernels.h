@@ -375,11 +375,15 @@ int roost_sink_attention(const void* qkv, int64_t ld, void* out, float* part, co
 
 /* ---- the Mamba selective scan (mamba1.cu) ---- */
 /* Per (row, channel): dt = softplus(dt_raw + dt_bias); S <- exp(dt a_neg) S + dt x B; y = S . C + d_skip x; out = y silu(z). xc
- * [tokens, inner]; dt_raw float[tokens, inner]; dbc rows [dt | B | C]; xz rows [x | z]; state slots [inner * n_state | ...]. */
+ * [tokens, inner]; dt_raw float[tokens, inner]; dbc rows [dt | B | C]; xz rows [x | z]; state slots [inner * n_state | ...].
+ * With ws_state (float[chunks * inner * n_state]) and ws_dt (float[chunks * inner]), chunks = roost_mamba1_scan_chunks(tokens,
+ * rows), rows are cut into chunks of 128 tokens that run side by side (three launches); with null pointers every row is walked
+ * in one pass. */
+int roost_mamba1_scan_chunks(int tokens, int rows);
 int roost_mamba1_scan(const void* xc, const float* dt_raw, const void* dbc, int64_t ld_dbc, const void* xz, int64_t ld_xz, void* out,
                       const float* dt_bias, const float* a_neg, const float* d_skip, float* state, int64_t state_stride,
-                      const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int inner, int n_state, int dt_rank, int dtype,
-                      roost_stream_t stream);
+                      const int32_t* q_indptr, const int32_t* slots, int rows, int tokens, int inner, int n_state, int dt_rank,
+                      float* ws_state, float* ws_dt, int dtype, roost_stream_t stream);
 
 #ifdef __cplusplus
 }

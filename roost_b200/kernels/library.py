@@ -142,7 +142,8 @@ _SIGNATURES = {
     "roost_sink_attention": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
     "roost_mamba1_scan": [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "roost_mamba1_scan_chunks": [c_int, c_int],
     "roost_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_argmax_split": [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -877,7 +878,8 @@ class KernelLibrary:
         return out
 
     # ------------------------------------------------------------------ the selective scan
-    def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, n_state, dt_rank) -> torch.Tensor:
+    def mamba1_scan(self, xc, dt, dbc, xz, dt_bias, a, d, state, q_indptr, slots, inner, n_state, dt_rank, chunked: bool | None = None) -> torch.Tensor:
+        """``chunked`` None: steps of ``SCAN_CHUNKED_MIN_TOKENS`` tokens or more cut their rows into chunks that run side by side."""
         _need(xc, "xc"); _need(dt, "dt", torch.float32); _need(dbc, "dbc", xc.dtype); _need(xz, "xz", xc.dtype); _need(state, "state", torch.float32)
         for n, t in (("dt_bias", dt_bias), ("A", a), ("D", d)):
             _need(t, n, torch.float32)
@@ -885,9 +887,14 @@ class KernelLibrary:
         if tuple(dt.shape) != (T, inner) or tuple(a.shape) != (inner, n_state) or xc.shape[1] != inner:
             raise KernelError("mamba1_scan: the step sizes, the decays or the convolution's output do not fit")
         out = torch.empty((T, inner), dtype=xc.dtype, device=xc.device)
+        ws_state = ws_dt = None
+        if (T >= self.SCAN_CHUNKED_MIN_TOKENS) if chunked is None else chunked:
+            chunks = self._lib.roost_mamba1_scan_chunks(T, slots.numel())
+            ws_state = torch.empty((chunks * inner * n_state,), dtype=torch.float32, device=xc.device)
+            ws_dt = torch.empty((chunks * inner,), dtype=torch.float32, device=xc.device)
         self._call("roost_mamba1_scan", _ptr(xc), _ptr(dt), _ptr(dbc), dbc.stride(0), _ptr(xz), xz.stride(0), _ptr(out), _ptr(dt_bias), _ptr(a),
                    _ptr(d), _ptr(state), state.stride(0), _ptr(q_indptr), _ptr(slots), slots.numel(), T, inner, n_state, dt_rank,
-                   dtype_code(xc.dtype), _stream())
+                   _ptr(ws_state), _ptr(ws_dt), dtype_code(xc.dtype), _stream(), launches=3 if ws_state is not None else 1)
         return out
 
     def attention_set_decode_tma(self, on: bool) -> None:

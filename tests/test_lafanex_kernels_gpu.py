@@ -354,3 +354,40 @@ def test_the_tensor_core_attention_kernels_with_a_sink_against_the_32_bit_kernel
         errs = [H.rms_error(results[tc]["a"][-1:], want_last) for tc in (True, False)]
         print(f"MEASURED without the sink the last position's logits move by {moved:.4f}; the kernels' errors there: {errs[0]:.2e}, {errs[1]:.2e}")
         assert moved > 8 * max(errs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inner,state", [(40, 16), (33, 24)])
+def test_long_rows_of_the_scan_cut_into_chunks_that_run_side_by_side(kernels, dtype, inner, state):
+    """Rows of 300, 1, 129, 128, 0 and 257 tokens on states that are not empty: the chunked form (a walk of every chunk from an
+    empty state, a carry from chunk to chunk, a second walk that writes the outputs) against one walk a row and the plain sum;
+    the slots end with the same states."""
+    g = torch.Generator().manual_seed(inner)
+    r = lambda *shape: torch.randn(*shape, generator=g)
+    rows, rank = [300, 1, 129, 128, 0, 257], 3
+    T = sum(rows)
+    indptr = [0]
+    for n in rows:
+        indptr.append(indptr[-1] + n)
+    slots = i32([4, 1, 0, 5, 2, 3])
+    a = -torch.exp(-3 + 2 * torch.rand(inner, state, generator=g))
+    dt_bias, d = -2 + 0.5 * r(inner), 1 + 0.3 * r(inner)
+    xc, dbc, xz, dt_raw = r(T, inner).to(dtype), r(T, rank + 2 * state).to(dtype), r(T, 2 * inner).to(dtype), r(T, inner)
+    start = r(6, inner * state)
+    states, outs = {}, {}
+    for chunked in (False, True):
+        st = start.clone().cuda()
+        outs[chunked] = kernels.mamba1_scan(xc.cuda(), dt_raw.cuda(), dbc.cuda(), xz.cuda(), dt_bias.cuda(), a.cuda(), d.cuda(), st, i32(indptr), slots,
+                                            inner, state, rank, chunked=chunked)
+        states[chunked] = st.cpu()
+    want, want_states = [], start.double().clone()
+    for b, slot in enumerate(slots.tolist()):
+        lo, hi = indptr[b], indptr[b + 1]
+        y, S = plain_scan(xc[lo:hi].double(), dt_raw[lo:hi].double(), dbc[lo:hi].double(), xz[lo:hi, inner:].double(), dt_bias.double(), a.double(),
+                          d.double(), start[slot].double().reshape(inner, state), rank, state)
+        want.append(y)
+        want_states[slot] = S.reshape(-1)
+    want = torch.cat(want)
+    for chunked in (False, True):
+        close(outs[chunked], want, dtype, f"scan, chunked {chunked}", f32=5e-5)
+        assert H.scaled_error(states[chunked], want_states) < 5e-5
