@@ -483,6 +483,27 @@ __global__ void moe_combine_weighted_kernel(const T* __restrict__ ys, const int3
   }
   __syncthreads();
   const float g = (shared != nullptr && gate != nullptr) ? 1.0f / (1.0f + expf(-gate[(size_t)t * gate_stride])) : 1.0f;
+  constexpr int V = Vec<T>::N;
+  if (hidden % V == 0 && (uintptr_t)ys % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (shared == nullptr || (uintptr_t)shared % 16 == 0)) {
+    for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {      // whole 16-byte vectors: the same sums in the same order
+      float acc[V], xv[V], v[V];
+      Vec<T>::load(x + (size_t)t * hidden + i, xv);
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[e] = 0.f;
+      for (int k = 0; k < top; ++k) {
+        if (!idk[k]) Vec<T>::load(ys + (size_t)rk[k] * hidden + i, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = fmaf(wk[k], idk[k] ? xv[e] : v[e], acc[e]);
+      }
+      if (shared) {
+        Vec<T>::load(shared + (size_t)t * hidden + i, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = fmaf(g, v[e], acc[e]);
+      }
+      Vec<T>::store(out + (size_t)t * hidden + i, acc);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float acc = 0.f;
     const float xv = to_float(x[(size_t)t * hidden + i]);
