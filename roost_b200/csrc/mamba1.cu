@@ -8,13 +8,13 @@
 //         projection's 32-bit output, x the convolution's output, [dt | B | C] rows of the projection of x, z the second half
 //         of the input projection's rows. S is read from and written to the row's slot. 32-bit throughout.
 // A channel's state is shared by L adjacent lanes (L a power of two, each lane keeps 8 state indices in registers); a block
-// of 128 threads takes 128 / L channels and stages 8 tokens of B, C, dt and x at a time. The float32 form computes the decay
+// of 128 threads takes 128 / L channels and stages 8 (decode steps) or 32 tokens of B, C, dt and x at a time. The float32 form computes the decay
 // exp(dt A) with a reduced-argument polynomial rounded to nearest instead of the special-function unit's exponential: that
 // unit's error (up to 2 units in the last place) leans one way for the small arguments of slow decays, and a state multiplied by
 // it a thousand times in a row drifts by that lean times a thousand, far above the rounding of everything else. Rows are given by q_indptr (token
 // range) and slots; the padding rows of a captured step name a scratch slot. Every sum's order depends on the sizes only.
 //
-// Steps of many tokens cut every row into chunks of 128 tokens that run side by side (three launches): each chunk but a row's
+// Steps of many tokens cut every row into chunks of 64 tokens that run side by side (three launches): each chunk but a row's
 // last walks its tokens from an empty state and leaves that state and the sum of its step sizes a channel; one thread a
 // (row, channel, state index) then carries the row's state from chunk to chunk, S <- exp(A sum dt) S + chunk's state, leaving every
 // chunk's true starting state in its place and the row's final state in the slot; a second walk of every chunk from its
@@ -24,7 +24,8 @@
 namespace roost {
 
 constexpr int kM1Threads = 128;
-constexpr int kM1Chunk = 8;
+constexpr int kM1Chunk = 8;          // tokens staged at once by a block that walks a decode step's rows
+constexpr int kM1ChunkLong = 32;     // ... and by a block that walks many tokens: four times fewer waits for the staged loads
 constexpr int kM1PerLane = 8;
 
 // exp(x) for x <= 0 to about one unit in the last place: x = j ln2 + r with ln2 in two parts, a degree-7 polynomial in r.
@@ -47,9 +48,9 @@ __device__ __forceinline__ float decay_exp(float x) { return expf(x); }
 template <>
 __device__ __forceinline__ float decay_exp<float>(float x) { return exp_nearest(x); }
 
-constexpr int kM1ChunkTokens = 128;
+constexpr int kM1ChunkTokens = 64;
 
-// Which (row, chunk) the block `b` of a chunked launch takes: rows in order, each with ceil(tokens / 128) chunks. False beyond
+// Which (row, chunk) the block `b` of a chunked launch takes: rows in order, each with ceil(tokens / 64) chunks. False beyond
 // the step's chunks.
 __device__ __forceinline__ bool chunk_of_block(const int32_t* __restrict__ q_indptr, int rows, int b, int& r, int& k, int& chunks_of_row) {
   for (r = 0; r < rows; ++r) {
@@ -75,15 +76,15 @@ __global__ void __launch_bounds__(kM1Threads) mamba1_scan_kernel(const T* __rest
                                                                 const float* __restrict__ d_skip, float* state, int64_t state_stride,
                                                                 const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ slots, int inner,
                                                                 int N, int R, int L, int rows, float* __restrict__ ws_state,
-                                                                float* __restrict__ ws_dt) {
+                                                                float* __restrict__ ws_dt, int stage_tokens) {
   extern __shared__ float sm[];
   const int NP = L * kM1PerLane;                 // state indices, padded
   const int CPB = kM1Threads / L;                // channels a block
   float* sB = sm;                                // [chunk][NP]
-  float* sC = sB + kM1Chunk * NP;                // [chunk][NP]
-  float* sdt = sC + kM1Chunk * NP;               // [chunk][CPB]
-  float* sx = sdt + kM1Chunk * CPB;              // [chunk][CPB]
-  float* sy = sx + kM1Chunk * CPB;               // [chunk][CPB]
+  float* sC = sB + stage_tokens * NP;            // [chunk][NP]
+  float* sdt = sC + stage_tokens * NP;           // [chunk][CPB]
+  float* sx = sdt + stage_tokens * CPB;          // [chunk][CPB]
+  float* sy = sx + stage_tokens * CPB;           // [chunk][CPB]
   pdl_launch_dependents();
   int r = blockIdx.x, k = 0, chunks_of_row = 1;
   if (MODE != 0 && !chunk_of_block(q_indptr, rows, blockIdx.x, r, k, chunks_of_row)) return;
@@ -106,15 +107,17 @@ __global__ void __launch_bounds__(kM1Threads) mamba1_scan_kernel(const T* __rest
   float dt_sum = 0.f;
 #pragma unroll
   for (int i = 0; i < kM1PerLane; ++i) S[i] = (MODE != 1 && live && n0 + i < N) ? Sg[n0 + i] : 0.f;
-  for (int t0 = start; t0 < end; t0 += kM1Chunk) {
-    const int nt = min(kM1Chunk, end - t0);
+  for (int t0 = start; t0 < end; t0 += stage_tokens) {
+    const int nt = min(stage_tokens, end - t0);
     __syncthreads();
+#pragma unroll 4      // several loads in flight a thread: a stage's time is its loads' latency
     for (int idx = threadIdx.x; idx < nt * NP; idx += kM1Threads) {
       const int tt = idx / NP, n = idx % NP;
       const T* row = dbc + (size_t)(t0 + tt) * ld_dbc + R;
       sB[idx] = n < N ? to_float(row[n]) : 0.f;
       sC[idx] = n < N ? to_float(row[N + n]) : 0.f;
     }
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < nt * CPB; idx += kM1Threads) {
       const int tt = idx / CPB, cc = c0 + idx % CPB;
       float dt = 0.f, x = 0.f;
@@ -145,6 +148,7 @@ __global__ void __launch_bounds__(kM1Threads) mamba1_scan_kernel(const T* __rest
     }
     if (MODE == 1) continue;
     __syncthreads();
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < nt * CPB; idx += kM1Threads) {
       const int tt = idx / CPB, cc = c0 + idx % CPB;
       if (cc < inner) {
@@ -213,22 +217,25 @@ extern "C" int roost_mamba1_scan(const void* xc, const float* dt_raw, const void
   const int cpb = kM1Threads / L;
   const int gy = (inner + cpb - 1) / cpb;
   if (gy > 65535 || rows > 65535) return fail(ROOST_ERR_UNSUPPORTED, "mamba1_scan: too many channels or rows");
-  const size_t smem = ((size_t)2 * kM1Chunk * L * kM1PerLane + (size_t)3 * kM1Chunk * cpb) * sizeof(float);
+  // steps of more tokens than rows stage 32 tokens at a time where that fits the default shared memory
+  int stage = kM1Chunk;
+  if (tokens > rows && ((size_t)2 * kM1ChunkLong * L * kM1PerLane + (size_t)3 * kM1ChunkLong * cpb) * sizeof(float) <= 48 * 1024) stage = kM1ChunkLong;
+  const size_t smem = ((size_t)2 * stage * L * kM1PerLane + (size_t)3 * stage * cpb) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   if (ws_state != nullptr) {
     const int chunks = roost_mamba1_scan_chunks(tokens, rows);
     ROOST_DISPATCH_DTYPE(dtype, T, {
       launch_kernel(mamba1_scan_kernel<T, 1>, dim3(chunks, gy), dim3(kM1Threads), smem, s, (const T*)xc, dt_raw, (const T*)dbc, ld_dbc, (const T*)xz,
-                    ld_xz, (T*)out, dt_bias, a_neg, d_skip, state, state_stride, q_indptr, slots, inner, n_state, dt_rank, L, rows, ws_state, ws_dt);
+                    ld_xz, (T*)out, dt_bias, a_neg, d_skip, state, state_stride, q_indptr, slots, inner, n_state, dt_rank, L, rows, ws_state, ws_dt, stage);
       launch_kernel(mamba1_carry_kernel<T>, dim3(rows, (inner * n_state + 255) / 256), dim3(256), 0, s, state, state_stride, ws_state,
                     (const float*)ws_dt, a_neg, q_indptr, slots, inner, n_state);
       launch_kernel(mamba1_scan_kernel<T, 2>, dim3(chunks, gy), dim3(kM1Threads), smem, s, (const T*)xc, dt_raw, (const T*)dbc, ld_dbc, (const T*)xz,
-                    ld_xz, (T*)out, dt_bias, a_neg, d_skip, state, state_stride, q_indptr, slots, inner, n_state, dt_rank, L, rows, ws_state, ws_dt);
+                    ld_xz, (T*)out, dt_bias, a_neg, d_skip, state, state_stride, q_indptr, slots, inner, n_state, dt_rank, L, rows, ws_state, ws_dt, stage);
     });
     return check_launch("mamba1_scan");
   }
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(mamba1_scan_kernel<T, 0>, dim3(rows, gy), dim3(kM1Threads), smem, s, (const T*)xc,
                                                dt_raw, (const T*)dbc, ld_dbc, (const T*)xz, ld_xz, (T*)out, dt_bias, a_neg, d_skip, state,
-                                               state_stride, q_indptr, slots, inner, n_state, dt_rank, L, rows, (float*)nullptr, (float*)nullptr));
+                                               state_stride, q_indptr, slots, inner, n_state, dt_rank, L, rows, (float*)nullptr, (float*)nullptr, stage));
   return check_launch("mamba1_scan");
 }

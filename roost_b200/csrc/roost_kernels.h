@@ -377,7 +377,7 @@ int roost_sink_attention(const void* qkv, int64_t ld, void* out, float* part, co
 /* Per (row, channel): dt = softplus(dt_raw + dt_bias); S <- exp(dt a_neg) S + dt x B; y = S . C + d_skip x; out = y silu(z). xc
  * [tokens, inner]; dt_raw float[tokens, inner]; dbc rows [dt | B | C]; xz rows [x | z]; state slots [inner * n_state | ...].
  * With ws_state (float[chunks * inner * n_state]) and ws_dt (float[chunks * inner]), chunks = roost_mamba1_scan_chunks(tokens,
- * rows), rows are cut into chunks of 128 tokens that run side by side (three launches); with null pointers every row is walked
+ * rows), rows are cut into chunks of 64 tokens that run side by side (three launches); with null pointers every row is walked
  * in one pass. */
 int roost_mamba1_scan_chunks(int tokens, int rows);
 int roost_mamba1_scan(const void* xc, const float* dt_raw, const void* dbc, int64_t ld_dbc, const void* xz, int64_t ld_xz, void* out,

@@ -24,7 +24,7 @@ constexpr int kSaWarps = 8;
 constexpr int kSaMaxDim = 512;
 
 template <typename T>
-__global__ void __launch_bounds__(512) sink_prepare_kernel(T* qkv, int64_t ld, T* q_out, T* k_base, T* v_base, int entry, const double* __restrict__ inv_freq,
+__global__ void __launch_bounds__(128) sink_prepare_kernel(T* qkv, int64_t ld, T* q_out, T* k_base, T* v_base, int entry, const double* __restrict__ inv_freq,
                                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
                                                           int heads, int kv_heads, int dim, int vdim, int rot_dims, float eps, int page_size) {
   extern __shared__ float sm[];      // rot_dims/2 cosines, rot_dims/2 sines
@@ -238,8 +238,8 @@ extern "C" int roost_sink_attention_prepare(void* qkv, int64_t ld, void* q_out, 
   if (dim > kSaMaxDim) return fail(ROOST_ERR_UNSUPPORTED, "sink_attention_prepare: heads beyond 512 numbers");
   if (tokens == 0) return ROOST_OK;
   const size_t smem = ((size_t)rot_dims + 2) * sizeof(float);
-  const int warps = heads + kv_heads < 4 ? 4 : (heads + kv_heads > 16 ? 16 : heads + kv_heads);      // a warp a head, up to sixteen at once
-  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(sink_prepare_kernel<T>, dim3(tokens), dim3(32 * warps), smem, (cudaStream_t)stream, (T*)qkv, ld, (T*)q_out, (T*)k_base,
+  // four warps a token: measured faster than a warp a head (sixteen warps: 30.7 against 19.6 us at 2,048 tokens of 16 + 4 heads of 64)
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(sink_prepare_kernel<T>, dim3(tokens), dim3(128), smem, (cudaStream_t)stream, (T*)qkv, ld, (T*)q_out, (T*)k_base,
                                                (T*)v_base, entry, inv_freq, positions, slot_mapping, heads, kv_heads, dim, vdim, rot_dims, eps,
                                                page_size));
   return check_launch("sink_attention_prepare");
