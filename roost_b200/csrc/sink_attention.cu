@@ -132,20 +132,23 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
   for (int c = 0; c < kSaMaxDim / 32; ++c) acc[c] = 0.f;
   const int n_tiles = pos / kSaTile + 1;
   const int first = z * tiles_per_split, last = min(n_tiles, first + tiles_per_split);
-  const int E = dim + vdim;
   for (int tile = first; tile < last; ++tile) {
     const int k0 = tile * kSaTile;
     __syncthreads();
-    for (int idx = threadIdx.x; idx < kSaTile * E; idx += blockDim.x) {
-      const int kk = idx / E, i = idx % E;
+    for (int kk = warp; kk < kSaTile; kk += kSaWarps) {      // a warp a key: its entry's address once, the lanes over its numbers
       const int kp = k0 + kk;
-      float v = 0.f;
+      float* kd = ks + (size_t)kk * (dim + 1);
+      float* vd = vs + (size_t)kk * vdim;
       if (kp <= pos) {
         const size_t at = (((size_t)pages[kp / page_size] * kv_heads + g) * page_size + kp % page_size) * entry;
-        v = i < dim ? to_float(k_base[at + i]) : to_float(v_base[at + i - dim]);
+        const T* kr = k_base + at;
+        const T* vr = v_base + at;
+        for (int i = lane; i < dim; i += 32) kd[i] = to_float(kr[i]);
+        for (int i = lane; i < vdim; i += 32) vd[i] = to_float(vr[i]);
+      } else {
+        for (int i = lane; i < dim; i += 32) kd[i] = 0.f;
+        for (int i = lane; i < vdim; i += 32) vd[i] = 0.f;
       }
-      if (i < dim) ks[(size_t)kk * (dim + 1) + i] = v;
-      else vs[(size_t)kk * vdim + i - dim] = v;
     }
     __syncthreads();
     if (!active) continue;
