@@ -155,7 +155,18 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
     const float* qw = qs + (size_t)warp * dim;
     const float* kr = ks + (size_t)lane * (dim + 1);
     float s = 0.f;
-    for (int i = 0; i < dim; ++i) s = fmaf(qw[i], kr[i], s);
+    if ((dim & 3) == 0) {        // the query four numbers a (broadcast) read; the same products in the same order
+      const float4* q4 = reinterpret_cast<const float4*>(qw);
+      for (int i = 0; i < dim / 4; ++i) {
+        const float4 qv = q4[i];
+        s = fmaf(qv.x, kr[4 * i], s);
+        s = fmaf(qv.y, kr[4 * i + 1], s);
+        s = fmaf(qv.z, kr[4 * i + 2], s);
+        s = fmaf(qv.w, kr[4 * i + 3], s);
+      }
+    } else {
+      for (int i = 0; i < dim; ++i) s = fmaf(qw[i], kr[i], s);
+    }
     s = k0 + lane <= pos ? s * scale : -INFINITY;
     const float m_new = fmaxf(m, warp_max(s));
     const float p = s > -INFINITY ? expf(s - m_new) : 0.f;
@@ -169,7 +180,15 @@ __global__ void __launch_bounds__(kSaWarps * 32) sink_attention_kernel(const T* 
       const int i = c * 32 + lane;
       if (i < vdim) {
         float a = acc[c] * keep;
-        for (int kk = 0; kk < kSaTile; ++kk) a = fmaf(ps[warp * kSaTile + kk], vs[(size_t)kk * vdim + i], a);
+        const float4* p4 = reinterpret_cast<const float4*>(ps + warp * kSaTile);
+#pragma unroll
+        for (int kk = 0; kk < kSaTile / 4; ++kk) {
+          const float4 pv = p4[kk];
+          a = fmaf(pv.x, vs[(size_t)(4 * kk) * vdim + i], a);
+          a = fmaf(pv.y, vs[(size_t)(4 * kk + 1) * vdim + i], a);
+          a = fmaf(pv.z, vs[(size_t)(4 * kk + 2) * vdim + i], a);
+          a = fmaf(pv.w, vs[(size_t)(4 * kk + 3) * vdim + i], a);
+        }
         acc[c] = a;
       }
     }
