@@ -32,8 +32,8 @@ class RoutedMlp(FeedForward):
         s = spec
         if min(s.hidden, s.experts, s.top, s.expert_intermediate) <= 0 or s.shared_intermediate < 0:
             raise ValueError("routed_mlp: hidden, experts, top and the experts' size must be positive")
-        if s.top > s.experts:
-            raise ValueError(f"routed_mlp: top {s.top} is more than the {s.experts} experts")
+        if s.top > s.experts + max(s.identity_experts, 0):
+            raise ValueError(f"routed_mlp: top {s.top} is more than the {s.experts} experts and {s.identity_experts} identity experts")
         if s.experts > 1024 or s.top > 32:
             raise ValueError("routed_mlp: more than 1024 experts or a top beyond 32 is more than the routing kernel serves")
         if s.activation not in GATE_FUNCTIONS:

@@ -120,6 +120,9 @@ SINGLE = {
     "scan_only": LM.config([(LM.mamba(inner=14, state=6, dt_rank=2, conv=4), None)], width=20, vocab=45, streams=4),
     "dense_after_attention": LM.config([(LM.attention(), LM.dense(ff=17))], width=28, vocab=33, streams=None),
     "experts_after_scan": LM.config([(LM.mamba(), LM.moe(experts=6, identity=1, top=2, ff=9, shared=11))], width=32, vocab=40, streams=2),
+    # more choices than experts with weights: at least two of a token's four choices are identity experts
+    "mostly_identity": LM.config([(LM.attention(heads=2, kv_heads=1, dim=8, vdim=8, rot=4), LM.moe(experts=2, identity=3, top=4, ff=10, shared=0))], width=24, vocab=41,
+                                 streams=3),
     "looped_pair": LM.config([(LM.attention(heads=2, kv_heads=1, dim=4, vdim=4, rot=2), None), (LM.mamba(inner=8, state=3, dt_rank=1, conv=2), None)],
                              width=16, vocab=30, streams=2, loop=(0, 2, 3)),
 }
