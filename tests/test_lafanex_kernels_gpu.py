@@ -269,7 +269,7 @@ def test_expert_products_with_the_clamped_swish_skip_identity_rows(kernels, dtyp
 
 # ------------------------------------------------------------------------------------------------ the sink on the tensor cores
 @pytest.mark.parametrize("faint", [False, True], ids=["random scores", "faint scores"])
-@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (128, 8, 2), (32, 2, 2)])
+@pytest.mark.parametrize("dim,heads,kv_heads", [(64, 4, 2), (128, 8, 2), (32, 2, 2), (64, 6, 2), (128, 5, 1), (256, 2, 1)])
 def test_the_tensor_core_attention_kernels_with_a_sink_against_the_32_bit_kernel(tmp_path, kernels, dim, heads, kv_heads, faint):
     """A one-layer model whose keys and values have one size runs its bfloat16 attention on the framework's tensor-core
     kernels with the sink added at their ends: a prompt of 700 tokens (the tcgen05 or mma.sync prefill), portions, three
