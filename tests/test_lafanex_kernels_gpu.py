@@ -391,3 +391,73 @@ def test_long_rows_of_the_scan_cut_into_chunks_that_run_side_by_side(kernels, dt
     for chunked in (False, True):
         close(outs[chunked], want, dtype, f"scan, chunked {chunked}", f32=5e-5)
         assert H.scaled_error(states[chunked], want_states) < 5e-5
+
+
+# ------------------------------------------------------------------------------------------------ the programs
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_tool_on_a_lafanex_folder(tmp_path, dtype):
+    """bin/trace_run finds the model by config.json and drives the engine's step function: a request cut into portions beside
+    another one, a step in which nothing is wanted, a request that ends and gives its pages and slot back."""
+    import json
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from tests import lafanex_models as LM
+    from tests.conftest import ROOT
+    cfg = LM.WIDE
+    tensors = LM.draw_tensors(cfg, 8)
+    folder = LM.write_model(tmp_path / "model", cfg, tensors)
+    a, b = H.random_ids(70, cfg["vocab"], 1), H.random_ids(41, cfg["vocab"], 2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:33], "want": [0, 32]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[:2], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[33:69], "want": [35]}, {"id": "b", "tokens": b[2:], "want": [38]}], "end": ["b"]},
+             {"step": 3, "entries": [{"id": "a", "tokens": a[69:], "want": [0]}], "end": ["a"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", "192"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [line for line in r.stdout.splitlines() if line.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    assert not (out / "1.f32").exists()
+    read = lambda n, rows: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(rows, cfg["vocab"]))
+    w = LM.plain_weights(tensors)
+    wa, wb = P.forward(cfg, w, a), P.forward(cfg, w, b)
+    bound = 2e-5 if dtype == "float32" else 0.05
+    assert H.rms_error(read(0, 2), wa[[0, 32]]) < bound
+    assert H.rms_error(read(2, 2), torch.stack([wa[68], wb[40]])) < bound
+    assert H.rms_error(read(3, 1), wa[69:70]) < bound
+
+
+def test_the_command_line_writes_a_lafanex_folder_and_generates_from_it(tmp_path):
+    """random-weights draws the folder from the configuration alone (decay rates, step biases and the streams' weights by their
+    declarations' hints), generate runs it through the entry point; the greedy tokens are the plain implementation's wherever
+    its choice is clear."""
+    import json
+    import subprocess
+    import sys
+
+    from roost_b200.weights.safetensors_io import SafetensorsFile
+    from tests import lafanex_models as LM
+    from tests.conftest import ROOT
+    roost = lambda *a: subprocess.run([sys.executable, str(ROOT / "bin" / "roost"), *a], capture_output=True, text=True, timeout=600)
+    (tmp_path / "config.json").write_text(json.dumps(LM.MIXED))
+    r = roost("random-weights", "--config", str(tmp_path / "config.json"), "--out", str(tmp_path / "model"), "--seed", "4", "--std", "0.1",
+              "--norm-std", "0.0")
+    assert r.returncode == 0, r.stderr
+    f = SafetensorsFile(tmp_path / "model" / "model.safetensors")
+    w = {n: f.tensor(n).clone().double() for n in f.names()}
+    assert tuple(w["l1.hc2.mix"].shape) == (3, 3) and float((w["l1.hc2.mix"] - torch.eye(3, dtype=torch.float64)).abs().max()) < 0.5
+    # the folder's norm weights are drawn around one, as the engine's other models store them; the design adds one to what is stored
+    cfg = LM.MIXED
+    prompt = H.random_ids(21, cfg["vocab"], 6)
+    r = roost("generate", "--model", str(tmp_path / "model"), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)),
+              "--max-output-tokens", "8", "--ignore-eos", "--attention-blocks", "16", "--max-sequences", "2")
+    assert r.returncode == 0, r.stderr
+    out = json.loads(r.stdout.strip().splitlines()[-1])
+    assert out["finish_reason"] == "length" and len(out["token_ids"]) == 8
+    logits = P.forward(cfg, w, prompt + out["token_ids"][:-1])
+    for j, tok in enumerate(out["token_ids"]):
+        top = logits[len(prompt) - 1 + j].topk(2)
+        if float(top.values[0] - top.values[1]) > 1e-3:
+            assert tok == int(top.indices[0]), (j, tok, int(top.indices[0]))
