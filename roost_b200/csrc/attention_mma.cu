@@ -52,6 +52,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// What rounding the pair to bfloat16 left over, as a second pair: with both as operands a product counts 16 bits of the values.
+__device__ __forceinline__ uint32_t pack_bf16_rest(float lo, float hi) {
+  return pack_bf16(lo - __bfloat162float(__float2bfloat16_rn(lo)), hi - __bfloat162float(__float2bfloat16_rn(hi)));
+}
 
 // Shared-memory tiles hold rows of D bfloat16 as 16-byte chunks, the chunk index xor-ed with the row so that the
 // eight rows an ldmatrix reads fall in different banks.
@@ -109,7 +113,7 @@ struct RowState {
 // the row).
 template <int D, int BN, typename L, typename QFrag>
 __device__ __forceinline__ void attend_core(RowState<D>& st, QFrag q_frag, uint32_t k_smem, uint32_t v_smem, int j0, const int (&qpos)[2],
-                                            const int (&qlo)[2], float scale_log2, int lane) {
+                                            const int (&qlo)[2], float scale_log2, int lane, bool wide = false) {
   constexpr int NT = BN / 8;
   float s[NT][4];
 #pragma unroll
@@ -191,12 +195,23 @@ __device__ __forceinline__ void attend_core(RowState<D>& st, QFrag q_frag, uint3
     const uint32_t a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
     const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
     const uint32_t a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;      // wide: the weights' remainders, a second operand of the same product
+    if (wide) {
+      r0 = pack_bf16_rest(s[2 * kk][0], s[2 * kk][1]);
+      r1 = pack_bf16_rest(s[2 * kk][2], s[2 * kk][3]);
+      r2 = pack_bf16_rest(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      r3 = pack_bf16_rest(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
 #pragma unroll
     for (int n2 = 0; n2 < D / 16; ++n2) {
       uint32_t b0, b1, b2, b3;
       ldmatrix_x4_trans(v_smem + L::offset(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)), b0, b1, b2, b3);
       mma_bf16(st.o[2 * n2], a0, a1, a2, a3, b0, b1);
       mma_bf16(st.o[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
+      if (wide) {
+        mma_bf16(st.o[2 * n2], r0, r1, r2, r3, b0, b1);
+        mma_bf16(st.o[2 * n2 + 1], r0, r1, r2, r3, b2, b3);
+      }
     }
   }
 }
@@ -204,13 +219,13 @@ __device__ __forceinline__ void attend_core(RowState<D>& st, QFrag q_frag, uint3
 // The same with the query rows q_row0..+15 of a shared-memory tile as the A operand and K/V tiles in the same layout.
 template <int D, int BN>
 __device__ __forceinline__ void attend_tile(RowState<D>& st, uint32_t q_smem, int q_row0, uint32_t k_smem, uint32_t v_smem, int j0,
-                                            const int (&qpos)[2], const int (&qlo)[2], float scale_log2, int lane) {
+                                            const int (&qpos)[2], const int (&qlo)[2], float scale_log2, int lane, bool wide = false) {
   attend_core<D, BN, Tile<D>>(
       st,
       [&](int kk, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
         ldmatrix_x4(q_smem + Tile<D>::offset(q_row0 + (lane & 15), kk * 2 + (lane >> 4)), a0, a1, a2, a3);
       },
-      k_smem, v_smem, j0, qpos, qlo, scale_log2, lane);
+      k_smem, v_smem, j0, qpos, qlo, scale_log2, lane, wide);
 }
 
 // The same for MT row tiles of 16 per warp: a key or value fragment loaded from shared memory feeds MT products, which is
@@ -226,7 +241,7 @@ struct RowStateM {
 template <int D, int BN, int MT>
 __device__ __forceinline__ void attend_tile_m(RowStateM<D, MT>& st, uint32_t q_smem, int q_row0, uint32_t k_smem, uint32_t v_smem,
                                               int key_row0, int j0, const int (&qpos)[MT][2], const int (&qlo)[MT][2], float scale_log2,
-                                              int lane) {
+                                              int lane, bool wide = false) {
   constexpr int NT = BN / 8;
   float s[MT][NT][4];
 #pragma unroll
@@ -325,6 +340,16 @@ __device__ __forceinline__ void attend_tile_m(RowStateM<D, MT>& st, uint32_t q_s
       a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
       a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
     }
+    uint32_t rest[MT][4];
+    if (wide) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        rest[mt][0] = pack_bf16_rest(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+        rest[mt][1] = pack_bf16_rest(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+        rest[mt][2] = pack_bf16_rest(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+        rest[mt][3] = pack_bf16_rest(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+      }
+    }
 #pragma unroll
     for (int n2 = 0; n2 < D / 16; ++n2) {
       uint32_t b0, b1, b2, b3;
@@ -333,6 +358,10 @@ __device__ __forceinline__ void attend_tile_m(RowStateM<D, MT>& st, uint32_t q_s
       for (int mt = 0; mt < MT; ++mt) {
         mma_bf16(st.o[mt][2 * n2], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
         mma_bf16(st.o[mt][2 * n2 + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+        if (wide) {
+          mma_bf16(st.o[mt][2 * n2], rest[mt][0], rest[mt][1], rest[mt][2], rest[mt][3], b0, b1);
+          mma_bf16(st.o[mt][2 * n2 + 1], rest[mt][0], rest[mt][1], rest[mt][2], rest[mt][3], b2, b3);
+        }
       }
     }
   }
@@ -366,7 +395,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
                                                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
                                                                 int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
   const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // one more term, 2^(0 - m), in every row's denominator
-  window &= ~ROOST_ATTENTION_SINK;
+  const bool wide = (window & ROOST_ATTENTION_WIDE_WEIGHTS) != 0;       // the weights enter P V as two bfloat16 operands
+  window &= ~(ROOST_ATTENTION_SINK | ROOST_ATTENTION_WIDE_WEIGHTS);
   constexpr int BM = 64 * MT, BN = 64, HALF = 32, NT = 128;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -443,7 +473,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
     for (int half = 0; half < BN / HALF; ++half) {
       const int j0 = t * BN + half * HALF;
       if (j0 <= warp_hi && j0 + HALF - 1 >= warp_lo) {  // uniform in the warp
-        attend_tile_m<D, HALF, MT>(st, q_smem, warp * 16 * MT, k_smem[stage], v_smem[stage], half * HALF, j0, qpos, qlo, scale_log2, lane);
+        attend_tile_m<D, HALF, MT>(st, q_smem, warp * 16 * MT, k_smem[stage], v_smem[stage], half * HALF, j0, qpos, qlo, scale_log2, lane, wide);
       }
     }
     __syncthreads();
@@ -482,7 +512,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
                             float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window,
                             int slot_limit) {
   const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // added where a row's result is final, never to a partial one
-  window &= ~ROOST_ATTENTION_SINK;
+  const bool wide = (window & ROOST_ATTENTION_WIDE_WEIGHTS) != 0;       // the weights enter P V as two bfloat16 operands
+  window &= ~(ROOST_ATTENTION_SINK | ROOST_ATTENTION_WIDE_WEIGHTS);
   constexpr int BN = kDecodeTileKeys, STAGES = kDecodeStages;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -563,7 +594,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
     cp_async_commit();
     cp_async_wait<STAGES - 1>();  // all but the newest STAGES - 1 groups are done: tile i has arrived
     __syncwarp();
-    attend_tile<D, BN>(st, q_smem, 0, cur, cur + kTileBytes, t * BN, qpos, qlo, scale_log2, lane);
+    attend_tile<D, BN>(st, q_smem, 0, cur, cur + kTileBytes, t * BN, qpos, qlo, scale_log2, lane, wide);
     __syncwarp();  // every lane is done with `cur` before a later iteration loads into it
   }
   cp_async_wait<0>();
@@ -689,7 +720,8 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
                                 const int4* __restrict__ work, int items, float* __restrict__ part_o, float* __restrict__ part_ml, int q_heads,
                                 int kv_heads, int page_size, float scale_log2, int window, int cluster_chunks) {
   const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // added where a row's result is final, never to a partial one
-  window &= ~ROOST_ATTENTION_SINK;
+  const bool wide = (window & ROOST_ATTENTION_WIDE_WEIGHTS) != 0;       // the weights enter P V as two bfloat16 operands
+  window &= ~(ROOST_ATTENTION_SINK | ROOST_ATTENTION_WIDE_WEIGHTS);
   // cluster_chunks = S > 0: the grid is clusters of S CTAs, one cluster a (row, key/value head), the row's work items S in
   // a row of the list (some of them empty); CTA r of a cluster takes the r-th, leaves its result in its own shared memory
   // and the CTAs combine the S results in chunk order, with the merge kernel's arithmetic, through distributed shared
@@ -973,7 +1005,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
       }
       attend_core<D, TK, L>(
           st, [&](int kk, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; },
-          k_tile, v_tile, j0, qpos, qlo, scale_log2, lane);
+          k_tile, v_tile, j0, qpos, qlo, scale_log2, lane, wide);
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(stage));
     }
@@ -1358,6 +1390,12 @@ extern "C" int roost_attention_prefill_tile_rows(int head_dim, int q_heads, int 
   return head_dim <= 128 && packed_rows * kv_heads >= kPrefillWideMinRows ? 128 : 64;
 }
 
+// The same for a caller that asks for wide weights (ROOST_ATTENTION_WIDE_WEIGHTS), which the mma.sync kernels serve.
+extern "C" int roost_attention_prefill_tile_rows_mma(int head_dim, int kv_heads, long long packed_rows) {
+  if (!roost_attention_mma_supported(head_dim)) return 0;
+  return head_dim <= 128 && packed_rows * kv_heads >= kPrefillWideMinRows ? 128 : 64;
+}
+
 // 1: prompt portions run the tcgen05 kernel where the sizes allow (the default); 0: always the mma.sync kernel.
 extern "C" void roost_attention_set_prefill_tc(int on) { set_prefill_tc(on != 0); }
 
@@ -1399,11 +1437,12 @@ extern "C" int roost_attention_prefill(const void* q, long long tokens, void* ou
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_prefill: q_heads must be a multiple of kv_heads");
   if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: more than 65535 key/value heads");
   if (items == 0) return ROOST_OK;
-  if ((tile_rows == 128 || tile_rows == 256) && tokens > 0 &&
+  if ((tile_rows == 128 || tile_rows == 256) && tokens > 0 && !(window & ROOST_ATTENTION_WIDE_WEIGHTS) &&
       prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, q)) {
     return launch_prefill_tc(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, tile_rows, q_heads, kv_heads,
                              head_dim, page_size, pool_pages, scale, window, (cudaStream_t)stream);
   }
+  ROOST_REQUIRE(tile_rows != 256 || !(window & ROOST_ATTENTION_WIDE_WEIGHTS), "attention_prefill: work items of 256 packed rows belong to the tcgen05 kernel, which takes no wide weights");
   if (tile_rows == 128) {
     switch (head_dim) {
       case 16: return launch_prefill<16, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);

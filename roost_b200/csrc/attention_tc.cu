@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(64 + NG * 128, 1)
                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work, int items, int q_heads, int kv_heads,
                                 int page_size, float scale_log2, int window) {
   const float sink = (window & ROOST_ATTENTION_SINK) ? 1.0f : 0.f;     // one more term, 2^(0 - m), in every row's denominator
-  window &= ~ROOST_ATTENTION_SINK;
+  window &= ~(ROOST_ATTENTION_SINK | ROOST_ATTENTION_WIDE_WEIGHTS);      // a caller that wants wide weights is not sent here
   using Cfg = TcCfg<D, NG>;
   constexpr int BM = kTcRows, TK = kTcKeys, KS = Cfg::kKStages, VS = Cfg::kVStages, NP = TK / RPC, CB = D / 64;
   constexpr uint32_t kQBytes = BM * D * 2;                  // one row group's Q tile

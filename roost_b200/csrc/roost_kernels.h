@@ -36,6 +36,11 @@ extern "C" {
 /* Added to the `window` argument of the tensor-core attention entry points (roost_attention_prefill, _decode, _decode_cluster,
  * _decode_static): the softmax's denominator gets one more term, exp(0 - maximum), a key of score 0 that has no value. */
 #define ROOST_ATTENTION_SINK (1 << 30)
+/* Also added to `window`: the softmax weights enter the second product as two bfloat16 operands, their rounding and what it left
+ * over, so that 16 bits of the 32-bit weights count (the denominator is summed from the 32-bit weights anyway). The mma.sync
+ * kernels serve it; plan the prefill's work items with roost_attention_prefill_tile_rows_mma. */
+#define ROOST_ATTENTION_WIDE_WEIGHTS (1 << 29)
+int roost_attention_prefill_tile_rows_mma(int head_dim, int kv_heads, long long packed_rows);
 
 typedef void* roost_stream_t;
 

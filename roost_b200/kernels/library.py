@@ -72,6 +72,7 @@ _SIGNATURES = {
     "roost_attention_mma_supported": [c_int],
     "roost_attention_prefill_tile_rows": [c_int, c_int, c_int, c_int, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong],
     "roost_attention_set_prefill_tc": [c_int],
+    "roost_attention_prefill_tile_rows_mma": [c_int, c_int, ctypes.c_longlong],
     "roost_attention_prefill": [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -356,10 +357,13 @@ class KernelLibrary:
     def attention_mma_supported(self, head_dim: int) -> bool:
         return bool(self._lib.roost_attention_mma_supported(int(head_dim)))
 
-    def attention_prefill_tile_rows(self, q_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor, packed_rows: int = 0) -> int:
+    def attention_prefill_tile_rows(self, q_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor, packed_rows: int = 0,
+                                    tensor_memory: bool = True) -> int:
         """Packed rows of a prefill work item (64 or 128) for these pools [pages, kv_heads, page_size, head_dim] and a step
         that brings ``packed_rows`` packed rows in all to the prefill kernels."""
         pages, nkv, page, d = k_pool.shape
+        if not tensor_memory:       # the mma.sync kernels' items (a caller that wants wide weights)
+            return int(self._lib.roost_attention_prefill_tile_rows_mma(d, nkv, int(packed_rows)))
         return int(self._lib.roost_attention_prefill_tile_rows(d, int(q_heads), nkv, page, pages, _ptr(k_pool), _ptr(v_pool), int(packed_rows)))
 
     def attention_set_prefill_tc(self, on: bool) -> None:
@@ -368,18 +372,21 @@ class KernelLibrary:
 
     attention_mma_sink = True    # the tensor-core kernels take a softmax with one added to its denominator (``sink``)
     ATTENTION_SINK = 1 << 30     # ROOST_ATTENTION_SINK of csrc/roost_kernels.h
+    ATTENTION_WIDE_WEIGHTS = 1 << 29
 
     def attention_mma(self, q, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, plan, scale: float,
-                      window: int | None, sink: bool = False) -> torch.Tensor:
+                      window: int | None, sink: bool = False, wide_weights: bool = False) -> torch.Tensor:
         """Tensor-core attention (bfloat16). ``plan``: an ``AttentionPlan`` whose work lists are on the device. ``sink``: one is
-        added to the softmax's denominator (a key of score 0 that has no value)."""
+        added to the softmax's denominator (a key of score 0 that has no value). ``wide_weights``: the softmax weights enter P V as two
+        bfloat16 operands (16 bits of the 32-bit weights); the plan's prefill items must then come from
+        ``attention_prefill_tile_rows(..., tensor_memory=False)``."""
         _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16)
         T, nq, d = q.shape
         _, nkv, page, d2 = k_pool.shape
         if d2 != d:
             raise KernelError("attention_mma: head_dim of q and of the pool differ")
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
-        w = (int(window) if window else 0) | (self.ATTENTION_SINK if sink else 0)
+        w = (int(window) if window else 0) | (self.ATTENTION_SINK if sink else 0) | (self.ATTENTION_WIDE_WEIGHTS if wide_weights else 0)
         if plan.prefill_items:
             self._call("roost_attention_prefill", _ptr(q), T, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
                        _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page,

@@ -9,6 +9,8 @@ projection over the concatenated heads.
 The cache is a paged group. When keys and values have the same size it has two planes (keys, values), the layout of the
 framework's tensor-core attention kernels, which then serve the bfloat16 steps with the sink added at their end; otherwise it
 has one plane whose entries are [key | value] of one key/value head, and the 32-bit kernel, which takes any sizes, reads that.
+On the tensor cores the 32-bit softmax weights enter P V as two bfloat16 operands, their rounding and what it left over (16 bits
+of the weights), which the mma.sync kernels serve; the denominator is summed from the 32-bit weights.
 """
 from __future__ import annotations
 
@@ -87,12 +89,12 @@ class SinkAttention(Mixer):
     def _attend_tensor_cores(self, q, batch, cache, tables):
         s, k = self.spec, self.rt.kernels
         group = s.num_heads // s.num_kv_heads
-        tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group)
+        tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group, tensor_memory=False)
         split_for = getattr(k, "decode_split_for", None)
         chunk, cluster = split_for(batch.num_rows, batch.kv_cap, cache.k_pool, cache.v_pool) if split_for and batch.kv_cap else (k.decode_chunk, 0)
         plan = batch.step_work(self, ("sink_attention", group, None, chunk, tile_rows, cluster))
         return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr, tables.kv_indices, plan,
-                               s.scale, None, sink=s.sink)
+                               s.scale, None, sink=s.sink, wide_weights=True)
 
     def step_class(self, row_counts):
         return ("short_rows", any(n <= SHORT_ROW_TOKENS for n in row_counts))
