@@ -185,6 +185,7 @@ __global__ void mamba1_carry_kernel(float* state, int64_t state_stride, float* _
   if (chunks == 0) return;
   const float a = a_neg[idx];
   float S = state[(size_t)slots[r] * state_stride + idx];
+#pragma unroll 4      // the chunks' own states and step sums do not depend on S: several loads in flight
   for (int k = 0; k < chunks; ++k) {
     float* w = ws_state + ((size_t)(first + k) * inner) * N + idx;
     const float own = k < chunks - 1 ? *w : 0.f;

@@ -15,7 +15,7 @@ namespace roost {
 constexpr int kMaxStreams = 8;
 
 template <typename T, int S>
-__global__ void __launch_bounds__(256) stream_step_kernel(float* streams, const T* __restrict__ y, const T* __restrict__ init_from,
+__global__ void __launch_bounds__(512) stream_step_kernel(float* streams, const T* __restrict__ y, const T* __restrict__ init_from,
                                                          const float* __restrict__ mix, const float* __restrict__ write,
                                                          const float* __restrict__ read, const float* __restrict__ norm_w,
                                                          const int32_t* __restrict__ rows, T* __restrict__ out, int width, float eps) {
@@ -115,7 +115,9 @@ static cudaError_t launch_stream_step(float* streams, const void* y, const void*
   const size_t smem = ((size_t)width + 32) * sizeof(float);
   auto kernel = stream_step_kernel<T, S>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  return launch_kernel(kernel, dim3(n_out), dim3(256), smem, stream, streams, (const T*)y, (const T*)init_from, mix, write, read, norm_w, rows,
+  // few rows (decode steps): twice the threads a token, half the trips to memory one after the other
+  const int threads = n_out <= 64 && width > 256 ? 512 : 256;
+  return launch_kernel(kernel, dim3(n_out), dim3(threads), smem, stream, streams, (const T*)y, (const T*)init_from, mix, write, read, norm_w, rows,
                        (T*)out, width, eps);
 }
 
